@@ -12,6 +12,8 @@ from typing import Optional
 from pagedserve_b200.config.registry import ConfigError
 
 SUPPORTED_DTYPES = ("float32", "bfloat16")
+# A model without a position table has no longest request of its own; block tables need some width.
+UNBOUNDED_MODEL_LEN = 32768
 ORCA_STRATEGY = "orca"
 SARATHI_STRATEGY = "sarathi"
 SUPPORTED_SCHEDULING_STRATEGIES = (ORCA_STRATEGY, SARATHI_STRATEGY)
@@ -30,6 +32,8 @@ class EngineConfig:
     strategy: str = ORCA_STRATEGY               # reference: main.py:265-270
     prefill_chunk_size: int = 16                # reference: main.py:271-276
     enable_cuda_graphs: bool = True             # reference: --disable-cuda-graphs, main.py:317-321
+    max_model_len: Optional[int] = None         # longest request; None: the model's own bound, or
+                                                # UNBOUNDED_MODEL_LEN for a model that has none
     device: str = "cuda:0"
 
     def __post_init__(self):
@@ -54,5 +58,7 @@ class EngineConfig:
                 f"unknown scheduling strategy {self.strategy!r}; choose one of "
                 f"{SUPPORTED_SCHEDULING_STRATEGIES}"
             )
+        if self.max_model_len is not None and self.max_model_len <= 0:
+            raise ConfigError("max_model_len must be positive")
         if self.prefill_chunk_size <= 0:
             raise ConfigError("prefill_chunk_size must be positive")   # reference: orca_scheduler.py:51-52

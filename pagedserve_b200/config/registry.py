@@ -2,8 +2,8 @@
 
 The reference selects a model with a string switch over three names
 (reference: main.py:22-25, 97-133).  Here one table maps the architecture
-name found in ``config.json`` (``architectures[0]``, falling back to
-``model_type``) to a typed configuration class and to a function that turns
+name found in ``config.json`` (``architectures[0]`` or ``architecture``, falling
+back to ``model_type``) to a typed configuration class and to a function that turns
 that configuration into a :class:`pagedserve_b200.models.spec.ModelSpec`.
 Adding an architecture is one ``register_architecture`` call; nothing else in
 the engine names a model.
@@ -91,6 +91,8 @@ def resolve_architecture(values: dict) -> Tuple[str, type, Callable]:
         name = architectures[0]
     elif isinstance(architectures, str):
         name = architectures
+    elif isinstance(values.get("architecture"), str):      # some designs write the one name under the singular key
+        name = values["architecture"]
     if name is None:
         model_type = values.get("model_type")
         if model_type in _MODEL_TYPES:

@@ -12,6 +12,8 @@
 // token_item[t] is the row of block_table that holds the pages of token t's request: the
 // request's slot where the table is kept by slot, the token's item where it is built per step.
 //   s = (q.k) * scale, softmax in float32, o = p.v
+//   softcap > 0: s <- softcap * tanh(s / softcap) before the softmax;
+//   sink (one float per head, or null): exp(sink[h]) joins the softmax's denominator and nothing else.
 //   (reference: src/model/paged_attention.py:262-295; src/kernels/triton_paged_attention.py:219-331)
 // Keys are visited in tiles of 32 aligned to absolute positions; warp w takes tiles with
 // tile % 4 == w; the four partial (max, sum, acc) states are merged in warp order. The
@@ -101,7 +103,8 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict
                             const T* __restrict__ k_pool, const T* __restrict__ v_pool, long long page_stride,
                             const int* __restrict__ token_item, const int* __restrict__ positions,
                             const int* __restrict__ block_table, int bt_stride,
-                            int n_heads, int n_kv_heads, int head_dim, int page_size, int window, float scale) {
+                            int n_heads, int n_kv_heads, int head_dim, int page_size, int window, float scale,
+                            float softcap, const float* __restrict__ sink) {
     extern __shared__ float smem[];
     float* q_s = smem;                                   // [head_dim]
     float* acc_s = smem + head_dim;                      // [ATT_WARPS][head_dim]
@@ -141,6 +144,7 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict
             float dot = 0.f;
             for (int d = 0; d < head_dim; ++d) dot = fmaf(q_s[d], to_float(kr[d]), dot);
             s = dot * scale;
+            if (softcap > 0.f) s = softcap * tanhf(s / softcap);
         }
         float m_new = fmaxf(m, warp_max(s));
         float corr = expf(m - m_new);          // m == -inf on the first tile -> 0
@@ -172,7 +176,9 @@ paged_attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict
     float big = m_s[0];
 #pragma unroll
     for (int w = 1; w < ATT_WARPS; ++w) big = fmaxf(big, m_s[w]);
-    float total = 0.f;
+    const float sink_h = sink ? sink[h] : -INFINITY;
+    big = fmaxf(big, sink_h);
+    float total = sink ? expf(sink_h - big) : 0.f;
     float wgt[ATT_WARPS];
 #pragma unroll
     for (int w = 0; w < ATT_WARPS; ++w) {
@@ -219,7 +225,8 @@ PS_EXPORT int ps_paged_attention_simt(const void* q, int q_stride, void* out, in
                                       const void* k_pool, const void* v_pool, long long page_stride,
                                       const int* token_item, const int* positions, const int* block_table,
                                       int bt_stride, int T, int n_heads, int n_kv_heads, int head_dim,
-                                      int page_size, int window, float scale, int dtype, void* stream) {
+                                      int page_size, int window, float scale, float softcap, const float* sink,
+                                      int dtype, void* stream) {
     if (T <= 0) return PS_OK;
     int rc = check_attention_sizes(n_heads, n_kv_heads, head_dim, page_size);
     if (rc) return rc;
@@ -231,12 +238,12 @@ PS_EXPORT int ps_paged_attention_simt(const void* q, int q_stride, void* out, in
         return ps::launch_pdl(ps::paged_attention_simt_kernel<float>, grid, dim3(ps::ATT_WARPS * 32), smem, s,
                               (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_pool,
                               (const float*)v_pool, page_stride, token_item, positions, block_table, bt_stride,
-                              n_heads, n_kv_heads, head_dim, page_size, window, scale);
+                              n_heads, n_kv_heads, head_dim, page_size, window, scale, softcap, sink);
     if (dtype == PS_BF16)
         return ps::launch_pdl(ps::paged_attention_simt_kernel<__nv_bfloat16>, grid, dim3(ps::ATT_WARPS * 32), smem, s,
                               (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
                               (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_stride, token_item,
                               positions, block_table, bt_stride, n_heads, n_kv_heads, head_dim, page_size, window,
-                              scale);
+                              scale, softcap, sink);
     return PS_ERR_UNSUPPORTED;
 }

@@ -23,6 +23,9 @@
 #define PS_ACT_NONE 0
 #define PS_ACT_GELU_TANH 1
 #define PS_ACT_GELU_ERF 2
+#define PS_ACT_RELU_SQUARED 3
+#define PS_ACT_SILU 4
+#define PS_ACT_TANH 5
 
 #define PS_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -47,9 +50,19 @@ __device__ __forceinline__ float gelu_tanh(float x) {
 __device__ __forceinline__ float gelu_erf(float x) {
     return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
 }
+// max(x, 0)^2
+__device__ __forceinline__ float relu_squared(float x) {
+    const float r = fmaxf(x, 0.f);
+    return r * r;
+}
+// x / (1 + exp(-x))
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
 __device__ __forceinline__ float apply_act(float x, int act) {
     if (act == PS_ACT_GELU_TANH) return gelu_tanh(x);
     if (act == PS_ACT_GELU_ERF) return gelu_erf(x);
+    if (act == PS_ACT_RELU_SQUARED) return relu_squared(x);
+    if (act == PS_ACT_SILU) return silu(x);
+    if (act == PS_ACT_TANH) return tanhf(x);
     return x;
 }
 

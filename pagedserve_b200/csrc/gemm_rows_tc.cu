@@ -294,7 +294,7 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             for (int j = 0; j < 4; ++j) {
                 v[j] += b[j];
                 if (act == PS_ACT_GELU_TANH) v[j] = sizeof(TOut) == 2 ? gelu_tanh_fast(v[j]) : gelu_tanh(v[j]);
-                else if (act == PS_ACT_GELU_ERF) v[j] = gelu_erf(v[j]);
+                else if (act != PS_ACT_NONE) v[j] = apply_act(v[j], act);
             }
             if (to_pages) {
                 const int p = kv.positions[t];

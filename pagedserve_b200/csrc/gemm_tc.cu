@@ -316,9 +316,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         if (act == PS_ACT_GELU_TANH) {
 #pragma unroll
                             for (int j = 0; j < 32; ++j) v[j] = sizeof(TOut) == 2 ? gelu_tanh_fast(v[j]) : gelu_tanh(v[j]);
-                        } else if (act == PS_ACT_GELU_ERF) {
+                        } else if (act != PS_ACT_NONE) {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
+                            for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], act);
                         }
                         // 16-byte pieces of the row, XOR-swizzled by the row as the tensor map expects
                         if constexpr (sizeof(TOut) == 2) {

@@ -1,0 +1,116 @@
+// Rotary position encoding fused with the cache write.
+//
+// One launch per attention layer and step, between the q|k(|v) projection and attention:
+//   * queries are turned in place;
+//   * keys are turned on their way into the key pages (the projection's buffer keeps them as projected);
+//   * values go into the value pages: the rows of `v`, or, when `v` is null, the keys as projected
+//     (a layer whose values are its unturned keys needs no value projection and no second buffer).
+//
+// The first rot_dims dimensions of every head turn, the rest pass. Pair i (i < rot_dims / 2) is
+//   (2i, 2i + 1)             interleaved = 1
+//   (i, i + rot_dims / 2)    interleaved = 0
+// and (a, b) at position p becomes (a cos t - b sin t, b cos t + a sin t), t = p * inv_freq[i].
+// Positions, angles, sines and products are float32 (inv_freq is a float32 table made on the host);
+// results are rounded once to the storage type.
+//
+// Cache layout of one cache layer: pool[page * page_stride + (g * page_size + offset) * head_dim + d].
+#include "common.cuh"
+
+namespace ps {
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rotary_cache_write_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride,
+                          const T* __restrict__ v, int v_stride, const float* __restrict__ inv_freq, int rot_dims,
+                          int interleaved, const int* __restrict__ token_row, const int* __restrict__ positions,
+                          const int* __restrict__ block_table, int bt_stride, T* __restrict__ k_pool,
+                          T* __restrict__ v_pool, long long page_stride, int n_heads, int n_kv_heads, int head_dim,
+                          int page_size) {
+    pdl_prologue();
+    q = pdl_fresh(q);
+    k = pdl_fresh(k);
+    v = pdl_fresh(v);
+    const int t = blockIdx.x;
+    const int p = positions[t];
+    const int half = rot_dims >> 1;
+    const int units = half + (head_dim - rot_dims);        // per head: turning pairs, then passing singles
+    long long page_base = -1;
+    if (k_pool) {
+        const int page = block_table[(size_t)token_row[t] * bt_stride + p / page_size];
+        if (page >= 0) page_base = (long long)page * page_stride + (long long)(p % page_size) * head_dim;
+    }
+    const float pos = (float)p;
+    T* q_row = q + (size_t)t * q_stride;
+    const T* k_row = k + (size_t)t * k_stride;
+    const int total = (n_heads + n_kv_heads) * units;
+    for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+        const int head = idx / units, unit = idx - head * units;
+        const bool is_query = head < n_heads;
+        const int g = head - n_heads;                      // key/value head when not a query
+        if (unit >= half) {                                // a dimension that does not turn
+            if (is_query || page_base < 0) continue;
+            const int d = rot_dims + (unit - half);
+            const T key = k_row[g * head_dim + d];
+            const long long dst = page_base + (long long)g * page_size * head_dim + d;
+            k_pool[dst] = key;
+            v_pool[dst] = v ? v[(size_t)t * v_stride + g * head_dim + d] : key;
+            continue;
+        }
+        const int da = interleaved ? 2 * unit : unit, db = interleaved ? 2 * unit + 1 : unit + half;
+        float sn, cs;
+        sincosf(pos * inv_freq[unit], &sn, &cs);
+        if (is_query) {
+            T* row = q_row + head * head_dim;
+            const float a = to_float(row[da]), b = to_float(row[db]);
+            row[da] = from_float<T>(a * cs - b * sn);
+            row[db] = from_float<T>(b * cs + a * sn);
+        } else if (page_base >= 0) {
+            const T* row = k_row + g * head_dim;
+            const T ka = row[da], kb = row[db];
+            const float a = to_float(ka), b = to_float(kb);
+            const long long dst = page_base + (long long)g * page_size * head_dim;
+            k_pool[dst + da] = from_float<T>(a * cs - b * sn);
+            k_pool[dst + db] = from_float<T>(b * cs + a * sn);
+            if (v) {
+                const T* vr = v + (size_t)t * v_stride + g * head_dim;
+                v_pool[dst + da] = vr[da];
+                v_pool[dst + db] = vr[db];
+            } else {
+                v_pool[dst + da] = ka;
+                v_pool[dst + db] = kb;
+            }
+        }
+    }
+}
+
+}  // namespace ps
+
+// q [T, n_heads * head_dim] is turned in place. k [T, n_kv_heads * head_dim] is read only. v may be null: the
+// values are then the keys as projected. k_pool null: nothing is written to pages (queries only).
+PS_EXPORT int ps_rotary_cache_write(void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride,
+                                    const float* inv_freq, int rot_dims, int interleaved, const int* token_row,
+                                    const int* positions, const int* block_table, int bt_stride, void* k_pool,
+                                    void* v_pool, long long page_stride, int T, int n_heads, int n_kv_heads,
+                                    int head_dim, int page_size, int dtype, void* stream) {
+    if (T <= 0) return PS_OK;
+    if (n_heads < 0 || n_kv_heads < 0 || head_dim <= 0 || rot_dims < 0 || rot_dims > head_dim || (rot_dims & 1))
+        return PS_ERR_BAD_ARGUMENT;
+    if (rot_dims > 0 && !inv_freq) return PS_ERR_BAD_ARGUMENT;
+    if (k_pool && (!v_pool || !token_row || !block_table || page_size <= 0)) return PS_ERR_BAD_ARGUMENT;
+    if (!positions || !q || !k) return PS_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int work = (n_heads + n_kv_heads) * (rot_dims / 2 + head_dim - rot_dims);
+    const int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
+    if (dtype == PS_F32)
+        return ps::launch_pdl(ps::rotary_cache_write_kernel<float>, dim3(T), dim3(threads), 0, s, (float*)q, q_stride,
+                              (const float*)k, k_stride, (const float*)v, v_stride, inv_freq, rot_dims, interleaved,
+                              token_row, positions, block_table, bt_stride, (float*)k_pool, (float*)v_pool,
+                              page_stride, n_heads, n_kv_heads, head_dim, page_size);
+    if (dtype == PS_BF16)
+        return ps::launch_pdl(ps::rotary_cache_write_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, s,
+                              (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride,
+                              (const __nv_bfloat16*)v, v_stride, inv_freq, rot_dims, interleaved, token_row, positions,
+                              block_table, bt_stride, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, page_stride,
+                              n_heads, n_kv_heads, head_dim, page_size);
+    return PS_ERR_UNSUPPORTED;
+}

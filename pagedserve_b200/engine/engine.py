@@ -13,7 +13,7 @@ import torch
 
 from pagedserve_b200.cache.budget import MIB, kv_cache_budget, pages_for_budget
 from pagedserve_b200.cache.manager import CacheManager
-from pagedserve_b200.config.engine_config import EngineConfig
+from pagedserve_b200.config.engine_config import UNBOUNDED_MODEL_LEN, EngineConfig
 from pagedserve_b200.config.registry import ModelConfig, load_config_dict, resolve_architecture
 from pagedserve_b200.engine.step import ModelRunner
 from pagedserve_b200.kernels.ops import Ops
@@ -36,6 +36,13 @@ class Engine:
         self.dtype = _TORCH_DTYPE[engine_config.dtype]
         _, _, builder = resolve_architecture(model_config.to_dict())
         self.spec = builder(model_config)
+        # the longest request: the model's bound (a position table), lowered by the engine's setting; a model
+        # without a bound of its own gets the setting or a default
+        own = self.spec.max_model_len
+        limit = engine_config.max_model_len
+        if limit is None and own > (1 << 24):
+            limit = UNBOUNDED_MODEL_LEN
+        self.spec.max_model_len = own if limit is None else min(own, limit)
         self.ops = Ops(self.dtype)
         env = PartEnv(ops=self.ops, dtype=self.dtype, device=self.device)
         self.model = Model(self.spec, env)

@@ -34,7 +34,8 @@ def build_parser() -> argparse.ArgumentParser:
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens live requests hold at any time (sizes the page pool)")
     parser.add_argument("--block-size", type=int, default=16, help="tokens per KV page (default 16)")
-    parser.add_argument("--max-num-seqs", type=int, default=16, help="request slots (default 16)")
+    parser.add_argument("--max-num-seqs", type=int, default=4,
+                        help="request slots, also slots of per-request state (default 4)")
     parser.add_argument("--disable-cuda-graphs", action="store_true")
     return parser
 
@@ -52,6 +53,7 @@ def run(args, stdin=None, stdout=None) -> int:
     pages = -(-args.max_tokens // args.block_size)
     config = EngineConfig(dtype=args.dtype, block_size=args.block_size, num_blocks=pages,
                           max_num_seqs=args.max_num_seqs, max_num_batched_tokens=4096,
+                          max_model_len=pages * args.block_size,       # no request outgrows the pool
                           enable_cuda_graphs=not args.disable_cuda_graphs)
     engine = Engine.from_folder(args.model, config)
     for line in stdin:

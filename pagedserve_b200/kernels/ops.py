@@ -18,7 +18,7 @@ from pagedserve_b200.kernels.build import load as _load_library
 
 PS_F32, PS_BF16 = 0, 1
 _DTYPE_CODE = {torch.float32: PS_F32, torch.bfloat16: PS_BF16}
-_ACT_CODE = {None: 0, "none": 0, "gelu_tanh": 1, "gelu_erf": 2}
+_ACT_CODE = {None: 0, "none": 0, "gelu_tanh": 1, "gelu_erf": 2, "relu_squared": 3, "silu": 4, "tanh": 5}
 _STATUS = {1: "bad argument", 2: "unsupported size or dtype", 3: "kernel launch failed"}
 
 _c_void_p = ctypes.c_void_p
@@ -75,7 +75,13 @@ _SIGNATURES = {
         "ps_layernorm": [_P, _P, _I, _I, _P, _P, _F, _I, _P, _I, _P],
         "ps_gemm_simt": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
         "ps_kv_append": [_P, _P, _I, _P, _P, _P, _I, _P, _P, _L, _I, _I, _I, _I, _I, _P],
-        "ps_paged_attention_simt": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+        "ps_paged_attention_simt": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _F, _P,
+                                    _I, _P],
+        "ps_rotary_cache_write": [_P, _I, _P, _I, _P, _I, _P, _I, _I, _P, _P, _P, _I, _P, _P, _L, _I, _I, _I, _I, _I,
+                                  _I, _P],
+        "ps_token_shift_mix": [_P, _I, _P, _I, _P, _L, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _P],
+        "ps_wkv_recurrence": [_P, _P, _P, _P, _P, _I, _P, _P, _F, _P, _I, _I, _P, _L, _I, _P, _P, _P, _I, _I, _I, _I,
+                              _I, _P],
         "ps_sample": [_P, _I, _I, _I, _P, _P, _P, _I, _P, _P],
         "ps_step_shape": [_I, _P, _P, _P, _I, _I, _I, _I, _P],
         "ps_step_fill": [_I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _L, _P, _I, _I, _I, _I, _P],
@@ -521,8 +527,14 @@ class Ops:
                                       self.code, _stream()), "kv_append")
 
     def paged_attention_simt(self, q, out, k_pool, v_pool, page_stride, token_item, positions, block_table,
-                             n_heads, n_kv_heads, head_dim, page_size, window, scale):
-        """out[t, h] = softmax(q[t,h] . K[<=pos]) V over the request's pages; CUDA cores."""
+                             n_heads, n_kv_heads, head_dim, page_size, window, scale, softcap=None, sink=None):
+        """out[t, h] = softmax(q[t,h] . K[<=pos]) V over the request's pages; CUDA cores.  ``softcap``:
+        scores become softcap * tanh(score / softcap); ``sink``: float32 [n_heads], exp(sink[h]) joins the
+        softmax's denominator."""
+        if sink is not None:
+            _require(sink, "sink", torch.float32)
+            if sink.numel() != n_heads:
+                raise KernelError("attention: one sink per query head")
         T = q.shape[0]
         _require(q, "q", self.dtype)
         _require(out, "out", self.dtype)
@@ -533,7 +545,7 @@ class Ops:
             _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pool), _ptr(v_pool),
             page_stride, _ptr(token_item), _ptr(positions), _ptr(block_table),
             block_table.stride(0), T, n_heads, n_kv_heads, head_dim,
-            page_size, window or 0, scale, self.code, _stream()),
+            page_size, window or 0, scale, float(softcap or 0.0), _ptr(sink), self.code, _stream()),
             "paged_attention_simt")
         return out
 
@@ -665,19 +677,101 @@ class Ops:
         return out
 
     def attention(self, q, k, v, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, scale,
-                  write_cache=True):
-        """Write the step's keys and values into the pages, then attend from the pages."""
+                  write_cache=True, softcap=None, sink=None):
+        """Write the step's keys and values into the pages, then attend from the pages.  ``softcap`` and
+        ``sink`` as in :meth:`paged_attention_simt`."""
         if write_cache:
             self.kv_append(k, v, ctx.token_slot, ctx.positions, layer.block_table, layer.k_pool, layer.v_pool,
                            layer.page_stride, n_kv_heads, head_dim, layer.page_size)
-        if self.dtype == torch.float32 or head_dim % 16 != 0:
+        from pagedserve_b200.kernels import tensorcore
+
+        if self.dtype == torch.float32 or head_dim % 16 != 0 or not tensorcore.attention_ok(softcap, sink):
             # the CUDA-core kernel takes every head size; the tensor-core kernels want multiples of 16
             return self.paged_attention_simt(q, out, layer.k_pool, layer.v_pool, layer.page_stride,
                                              ctx.token_slot, ctx.positions, layer.block_table, n_heads,
-                                             n_kv_heads, head_dim, layer.page_size, window, scale)
-        from pagedserve_b200.kernels import tensorcore
+                                             n_kv_heads, head_dim, layer.page_size, window, scale, softcap, sink)
+        return tensorcore.attention(self, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, scale,
+                                    softcap=softcap, sink=sink)
 
-        return tensorcore.attention(self, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, scale)
+    # ------------------------------------------------------------------ rotary positions + cache write
+    def rotary_cache_write(self, q, k, v, inv_freq, rot_dims, interleaved, ctx, layer, n_heads, n_kv_heads,
+                           head_dim, write_cache=True):
+        """Turn the queries in place by position and send the step's keys (turned) and values into the pages
+        in one launch.  ``q`` [T, n_heads * head_dim], ``k`` [T, n_kv_heads * head_dim] (row views);
+        ``v`` None: the values are the keys as projected, before they are turned.  ``inv_freq``: float32
+        [rot_dims / 2]; the first ``rot_dims`` dimensions of a head turn, as neighbours (2i, 2i + 1) when
+        ``interleaved`` else as (i, i + rot_dims / 2)."""
+        T = q.shape[0]
+        _require(q, "q", self.dtype)
+        _require(k, "k", self.dtype)
+        if v is not None:
+            _require(v, "v", self.dtype)
+        if rot_dims:
+            _require(inv_freq, "inv_freq", torch.float32)
+            if inv_freq.numel() != rot_dims // 2:
+                raise KernelError("rotary: one frequency per pair of turning dimensions")
+        if q.stride(1) != 1 or k.stride(1) != 1 or (v is not None and v.stride(1) != 1):
+            raise KernelError("rotary: innermost stride must be 1")
+        if q.shape[1] != n_heads * head_dim or k.shape[1] != n_kv_heads * head_dim:
+            raise KernelError("rotary: widths do not match the head counts")
+        pools = write_cache and layer is not None and layer.k_pool is not None
+        if pools:
+            _require(layer.k_pool, "k_pool", self.dtype)
+        self.launches += 1
+        _check(self.core.ps_rotary_cache_write(
+            _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0) if v is not None else 0,
+            _ptr(inv_freq) if rot_dims else None, rot_dims, 1 if interleaved else 0,
+            _ptr(ctx.token_slot) if pools else None, _ptr(ctx.positions),
+            _ptr(layer.block_table) if pools else None, layer.block_table.stride(0) if pools else 0,
+            _ptr(layer.k_pool) if pools else None, _ptr(layer.v_pool) if pools else None,
+            layer.page_stride if pools else 0, T, n_heads, n_kv_heads, head_dim,
+            layer.page_size if pools else 1, self.code, _stream()), "rotary_cache_write")
+
+    # ------------------------------------------------------------------ linear recurrence with decay ("wkv")
+    def token_shift_mix(self, x, mu, state, prev_offset, ctx, out):
+        """out[s, t] = x[t] + (x[t-1] - x[t]) * mu[s]: ``x`` [T, W] (compute dtype), ``mu`` float32 [S, W],
+        ``out`` [S, T, W]; x[t-1] of an entry's first token is the request's stored last input
+        (``state[slot, prev_offset:prev_offset + W]``, float32)."""
+        T, W = x.shape
+        _require(x, "x", self.dtype)
+        _require(out, "out", self.dtype)
+        _require(mu, "mu", torch.float32)
+        _require(state, "state", torch.float32)
+        if out.shape != (mu.shape[0], T, W) or not out.is_contiguous() or x.stride(1) != 1 or mu.shape[1] != W:
+            raise KernelError("token_shift_mix: shapes do not match")
+        self.launches += 1
+        _check(self.core.ps_token_shift_mix(_ptr(x), x.stride(0), _ptr(mu), mu.shape[0], _ptr(state),
+                                            state.stride(0), prev_offset, _ptr(ctx.token_item), _ptr(ctx.q_start),
+                                            _ptr(ctx.item_slot), _ptr(out), out.stride(0), out.stride(1), T, W,
+                                            self.code, _stream()), "token_shift_mix")
+        return out
+
+    def wkv_recurrence(self, r, k, v, decay, gate, u, gain, eps, x, state, prev_offset, ctx, out, heads, head_dim):
+        """The recurrence of every entry of the step, tokens in order, from and into the slots' state (see
+        csrc/wkv.cu).  ``r, k, v, decay, gate``: float32 [T, heads * head_dim] of equal row stride; ``u``,
+        ``gain``: float32 [heads * head_dim]; ``x`` [T, W] the mixer's input, whose newest row per entry is
+        kept in the slot; ``out`` [T, heads * head_dim] in the compute dtype."""
+        inner = heads * head_dim
+        for name, tensor in (("r", r), ("k", k), ("v", v), ("decay", decay), ("gate", gate)):
+            _require(tensor, name, torch.float32)
+            if tensor.shape[1] != inner or tensor.stride(1) != 1 or tensor.stride(0) != r.stride(0):
+                raise KernelError("wkv: r, k, v, decay and gate must be rows of equal stride")
+        _require(u, "u", torch.float32)
+        _require(gain, "gain", torch.float32)
+        _require(state, "state", torch.float32)
+        _require(x, "x", self.dtype)
+        _require(out, "out", self.dtype)
+        if u.numel() != inner or gain.numel() != inner or state.shape[1] < prev_offset + x.shape[1]:
+            raise KernelError("wkv: sizes do not match")
+        if head_dim > 128:
+            raise KernelError("wkv: head sizes above 128 are not supported")
+        self.launches += 1
+        _check(self.core.ps_wkv_recurrence(_ptr(r), _ptr(k), _ptr(v), _ptr(decay), _ptr(gate), r.stride(0), _ptr(u),
+                                           _ptr(gain), float(eps), _ptr(x), x.stride(0), x.shape[1], _ptr(state),
+                                           state.stride(0), prev_offset, _ptr(ctx.q_start), _ptr(ctx.item_slot),
+                                           _ptr(out), out.stride(0), ctx.num_items, heads, head_dim, self.code,
+                                           _stream()), "wkv_recurrence")
+        return out
 
     # ------------------------------------------------------------------ sampling
     def sample(self, logits, temperature, seed, position, out, pos_offset=0):

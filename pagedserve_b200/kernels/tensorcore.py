@@ -51,7 +51,12 @@ def linear(ops, a, w, bias, out, act=None, accumulate=False, status=None):
     return ops.linear_simt(a, w, bias, out, act, accumulate)
 
 
-def attention(ops, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, scale):
+def attention_ok(softcap, sink) -> bool:
+    """Whether the tensor-core attention kernels compute this form of the softmax."""
+    return not softcap and sink is None
+
+
+def attention(ops, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, scale, softcap=None, sink=None):
     """Short entries (fewer than ``ctx.LONG_ENTRY`` tokens: decode tokens, short portions) come first in the
     step's flat batch and go token by token through the split-key kernel; long portions go through the
     tensor-core prefill kernel in blocks of 64 queries."""

@@ -94,3 +94,88 @@ class CausalSelfAttention(Mixer):
         ops.attention(q, k, v, context, ctx, layer, p["n_heads"], p["n_kv_heads"], p["head_dim"],
                       p.get("window"), float(p["scale"]), write_cache=write_cache and not written)
         ops.linear(context, self.w_out, self.b_out, residual, accumulate=True)
+
+
+@register_part("mixer", "rotary_attention")
+class RotaryAttention(Mixer):
+    """Attention with separate projections, rotary positions of its own, and optional extras of the softmax.
+
+    q = x W_q, k = x W_k, v = x W_v, or, without ``v_name``, v = k as projected (before it is turned): such a
+    layer has no value projection.  Queries and keys turn by position (``rotary``: dims, base, interleaved);
+    s = (q . k) * scale; with ``softcap`` c: s <- c * tanh(s / c); query i sees keys j with
+    0 <= i - j < ``window`` (all earlier keys without a window); with ``sink_name`` every query head has a
+    learned number whose exponential is added to the softmax's denominator and to nothing else;
+    residual += o W_o.  Scores, softmax, angles: float32.
+
+    The projections run as one product over the stacked matrices; one kernel then turns the queries in place
+    and sends the turned keys and the values into the pages; attention reads only pages.
+
+    params: hidden_size, n_heads, n_kv_heads, head_dim, scale, window, softcap, rotary (dict or None),
+    q_name, k_name, v_name (None: values are the unturned keys), out_name, sink_name (None: no sinks),
+    init_std, out_init_std.
+    """
+
+    graph_safe = True
+    accepts_deferred_norm = True       # x goes straight into ops.linear
+
+    def __init__(self, params, prefix, env):
+        super().__init__(params, prefix, env)
+        p = self.params
+        if p["n_heads"] % p["n_kv_heads"] != 0:
+            raise ValueError("n_heads must be a multiple of n_kv_heads")
+        if not (0 < p["head_dim"] <= 256):
+            raise ValueError(f"head_dim {p['head_dim']} is not supported: at most 256")
+        if p.get("window") is not None and p["window"] <= 0:
+            raise ValueError("window must be positive")
+        self.q_width = p["n_heads"] * p["head_dim"]
+        self.kv_width = p["n_kv_heads"] * p["head_dim"]
+        self.has_v = p.get("v_name") is not None
+        rotary = p.get("rotary") or dict(dims=0, base=10000.0)
+        from pagedserve_b200.parts.positions import RotaryPositions
+
+        self.rotary = RotaryPositions(dict(dims=rotary["dims"], base=rotary["base"],
+                                           interleaved=rotary.get("interleaved", True), head_dim=p["head_dim"]),
+                                      prefix, env)
+
+    def cache_need(self):
+        p = self.params
+        return KVNeed(p["n_kv_heads"], p["head_dim"], p.get("window"))
+
+    def param_specs(self):
+        p = self.params
+        std = p.get("init_std", 0.02)
+        specs = [(ParamSpec(self._n(p["q_name"]), (self.q_width, p["hidden_size"]), "matmul"), ("normal", std)),
+                 (ParamSpec(self._n(p["k_name"]), (self.kv_width, p["hidden_size"]), "matmul"), ("normal", std))]
+        if self.has_v:
+            specs.append((ParamSpec(self._n(p["v_name"]), (self.kv_width, p["hidden_size"]), "matmul"),
+                          ("normal", std)))
+        specs.append((ParamSpec(self._n(p["out_name"]), (p["hidden_size"], self.q_width), "matmul"),
+                      ("normal", p.get("out_init_std", std))))
+        if p.get("sink_name"):
+            specs.append((ParamSpec(self._n(p["sink_name"]), (p["n_heads"],), "vector"), ("normal", 1.0)))
+        return specs
+
+    def bind(self, tensors):
+        p = self.params
+        pieces = [tensors[self._n(p["q_name"])], tensors[self._n(p["k_name"])]]
+        if self.has_v:
+            pieces.append(tensors[self._n(p["v_name"])])
+        self.w_in = torch.cat(pieces, dim=0).contiguous()              # [q + k (+ v), H]
+        self.w_out = tensors[self._n(p["out_name"])]
+        self.sink = tensors[self._n(p["sink_name"])].contiguous() if p.get("sink_name") else None
+
+    def forward(self, x, residual, ctx, layer):
+        p = self.params
+        ops = self.env.ops
+        tokens = x.shape[0]
+        projected = ops.empty((tokens, self.w_in.shape[0]), self.env.dtype, residual.device)
+        ops.linear(x, self.w_in, None, projected)
+        q = projected[:, :self.q_width]
+        k = projected[:, self.q_width:self.q_width + self.kv_width]
+        v = projected[:, self.q_width + self.kv_width:] if self.has_v else None
+        self.rotary.turn_and_store(q, k, v, ctx, layer, p["n_heads"], p["n_kv_heads"],
+                                   write_cache=p.get("write_cache", True))
+        context = ops.empty((tokens, self.q_width), self.env.dtype, residual.device)
+        ops.attention(q, k, v, context, ctx, layer, p["n_heads"], p["n_kv_heads"], p["head_dim"], p.get("window"),
+                      float(p["scale"]), write_cache=False, softcap=p.get("softcap"), sink=self.sink)
+        ops.linear(context, self.w_out, None, residual, accumulate=True)

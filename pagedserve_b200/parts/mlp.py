@@ -7,14 +7,15 @@ import torch
 from pagedserve_b200.parts.base import FeedForward, register_part
 from pagedserve_b200.weights.loader import ParamSpec
 
-ACTIVATIONS = ("gelu_tanh", "gelu_erf")
+ACTIVATIONS = ("gelu_tanh", "gelu_erf", "relu_squared", "silu")
 
 
 @register_part("feed_forward", "dense_mlp")
 class DenseMLP(FeedForward):
     """residual += act(x W_up + b_up) W_down + b_down
     (reference: src/model/paged_decoder.py:178-179, 224-228, 273-280).
-    params: hidden_size, inner_size, activation ('gelu_tanh' | 'gelu_erf'), has_bias,
+    params: hidden_size, inner_size, activation ('gelu_tanh' | 'gelu_erf' | 'relu_squared' = max(z, 0)^2 | 'silu'),
+    has_bias,
     stored_in_out, up_name, down_name, init_std, out_init_std."""
 
     graph_safe = True
@@ -55,3 +56,14 @@ class DenseMLP(FeedForward):
         inner = ops.empty((x.shape[0], p["inner_size"]), self.env.dtype, x.device)
         ops.linear(x, self.w_up, self.b_up, inner, act=p["activation"])
         ops.linear(inner, self.w_down, self.b_down, residual, accumulate=True)
+
+
+@register_part("feed_forward", "none")
+class NoFeedForward(FeedForward):
+    """A layer without a feed-forward sublayer: no tensors, no work (the block skips its second norm too)."""
+
+    graph_safe = True
+    is_empty = True
+
+    def forward(self, x, residual, ctx):
+        return None

@@ -30,15 +30,18 @@ class LayerNorm(Norm):
 
     reference: nn.LayerNorm at src/model/paged_decoder.py:170-177, 291-294 and the
     fused kernel src/kernels/triton_residual_layernorm.py:25-40.
-    params: width, eps, name, has_mean (False gives the RMS form), has_bias, init_std.
+    params: width, eps, name, has_mean (False gives the RMS form), has_bias, init_std,
+    weight_offset (a constant added to the stored weight once, in float32, when it is bound: 1.0 for
+    gains that are stored as their distance from one; random weights are then drawn around zero).
     """
 
     graph_safe = True
 
     def param_specs(self):
         p = self.params
+        centred = bool(p.get("weight_offset"))
         specs = [(ParamSpec(self._n(p["name"] + ".weight"), (p["width"],), "vector"),
-                  ("ones_plus_normal", p.get("init_std", 0.0)))]
+                  ("normal" if centred else "ones_plus_normal", p.get("init_std", 0.0)))]
         if p.get("has_bias", True):
             specs.append((ParamSpec(self._n(p["name"] + ".bias"), (p["width"],), "vector"),
                           ("normal", p.get("init_std", 0.0))))
@@ -47,6 +50,8 @@ class LayerNorm(Norm):
     def bind(self, tensors):
         p = self.params
         self.weight = tensors[self._n(p["name"] + ".weight")]
+        if p.get("weight_offset"):
+            self.weight = self.weight + float(p["weight_offset"])        # float32: the "vector" role
         self.bias = tensors[self._n(p["name"] + ".bias")] if p.get("has_bias", True) else None
 
     def defer(self, x, rows=None):

@@ -34,3 +34,44 @@ class NoPositions(PositionEncoding):
     """No position information at all."""
 
     graph_safe = True
+
+
+@register_part("positions", "rotary")
+class RotaryPositions(PositionEncoding):
+    """Queries and keys turn by their position: of the first ``dims`` dimensions of every head, pair i turns by
+    the angle position * base^(-2i / dims); the other dimensions pass unchanged.  ``interleaved`` pairs
+    neighbours (2i, 2i + 1), otherwise dimension i goes with i + dims / 2.  Angles, sines and products are
+    float32; the table of frequencies is made on the host in float64 and rounded once.
+
+    A model may name it as its position encoding (``rotate`` is then called by the attention mixers), or a
+    mixer with constants of its own builds one for itself.  Keys reach the cache turned: the kernel that turns
+    them also writes the pages (``turn_and_store``).
+    params: dims, base, interleaved, head_dim."""
+
+    graph_safe = True
+
+    def __init__(self, params, prefix, env):
+        super().__init__(params, prefix, env)
+        p = self.params
+        if p["dims"] < 0 or p["dims"] % 2 or p["dims"] > p["head_dim"]:
+            raise ValueError("rotary: dims must be even and at most the head size")
+        if not p["base"] > 0:
+            raise ValueError("rotary: base must be positive")
+        self._inv_freq = None
+
+    def inv_freq(self):
+        if self._inv_freq is None:
+            import torch
+
+            dims = self.params["dims"]
+            exponent = -2.0 * torch.arange(dims // 2, dtype=torch.float64) / max(dims, 1)
+            table = torch.pow(torch.tensor(float(self.params["base"]), dtype=torch.float64), exponent)
+            self._inv_freq = table.to(torch.float32).to(self.env.device)
+        return self._inv_freq
+
+    def turn_and_store(self, q, k, v, ctx, layer, n_heads, n_kv_heads, write_cache=True):
+        """Turn ``q`` in place; write the turned keys and the values (``v``, or the unturned keys when ``v`` is
+        None) into the pages of ``layer``."""
+        p = self.params
+        self.env.ops.rotary_cache_write(q, k, v, self.inv_freq(), p["dims"], p.get("interleaved", True), ctx, layer,
+                                        n_heads, n_kv_heads, p["head_dim"], write_cache=write_cache)

@@ -46,7 +46,7 @@ class WeightError(ValueError):
 @dataclass(frozen=True)
 class ParamSpec:
     name: str                         # canonical checkpoint name
-    shape: Tuple[int, ...]            # shape as stored in the file
+    shape: Tuple[int, ...]            # shape as stored in the file; -1: any extent (a size that only the file gives)
     role: str = "matmul"
     transpose: bool = False           # store [in,out] -> keep [out,in]
     optional: bool = False            # may be absent (e.g. a tied head)
@@ -101,7 +101,8 @@ def place_tensors(
         tensor = canonical.get(name)
         if tensor is None:
             continue
-        if tuple(tensor.shape) != tuple(spec.shape):
+        if len(tensor.shape) != len(spec.shape) or any(
+                want >= 0 and want != got for want, got in zip(spec.shape, tensor.shape)):
             wrong_shape.append((origin[name], tuple(spec.shape), tuple(tensor.shape)))
         if spec.role == "index":
             if tensor.dtype.is_floating_point:
