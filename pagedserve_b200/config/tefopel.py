@@ -136,7 +136,7 @@ class TefopelConfig(ModelConfig):
 
 
 def attention_layer(heads: int, kv_heads: int, dim: int, window: int, ff: Optional[int], rot_dims: Optional[int] = None,
-                    base: float = 10000.0, scale: Optional[float] = None, softcap: float = 30.0) -> dict:
+                    base: float = 10000.0, scale: Optional[float] = None, softcap: float = 50.0) -> dict:
     """A layer entry as config.json writes it (for random models: benchmarks, tests, the command line)."""
     return {"type": "attention",
             "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim,

@@ -122,7 +122,7 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                               float* __restrict__ part_acc, float* __restrict__ part_ml,
                               int* __restrict__ counters, int* __restrict__ status,
                               const int* __restrict__ q_start, const int* __restrict__ kv_len, int cluster,
-                              const int* __restrict__ token_row) {
+                              const int* __restrict__ token_row, SoftmaxExtras extras) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     // page_size, chunk_keys and the unit are powers of two: shifts and masks instead of divisions
     const int unit = min(page_size, chunk_keys >> 3);                                // keys per copy
@@ -240,7 +240,9 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     float o_acc[OT][4];
 #pragma unroll
     for (int i = 0; i < OT; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    // the sink starts the state of one team of the (token, head) pair: team 0 of the first split with keys
+    const bool takes_sink = extras.sink && active && split == first_split && grp == 0;
+    float m_run = takes_sink ? extras.sink[h] * 1.4426950408889634f : -INFINITY, l_run = takes_sink ? 1.f : 0.f;
     const int key_tiles = chunk_keys >> 4;
     const int unit_mask = n_units - 1;
     // MMA row m of a chunk is key (m % n_units) * unit + m / n_units and lies at element
@@ -290,8 +292,8 @@ paged_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                 }
                 const int ka = row_key(16 * mt + gq), kb = row_key(16 * mt + gq + 8);   // MMA rows -> keys of the chunk
                 if (tq == 0 && ok) {
-                    if (ka >= j_lo && ka <= j_hi) sc[i][0] = c[0] * scale_log2;
-                    if (kb >= j_lo && kb <= j_hi) sc[i][1] = c[2] * scale_log2;
+                    if (ka >= j_lo && ka <= j_hi) sc[i][0] = score_log2(c[0], scale_log2, extras);
+                    if (kb >= j_lo && kb <= j_hi) sc[i][1] = score_log2(c[2], scale_log2, extras);
                 }
                 wmax = fmaxf(wmax, fmaxf(sc[i][0], sc[i][1]));
             }
@@ -553,7 +555,9 @@ static int launch_attention_decode(const void* q, int q_stride, void* out, int o
                                    int n_kv_heads, int head_dim, int page_size, int window, float scale,
                                    int split_tiles, int n_splits, float* part_acc, float* part_ml, int* counters,
                                    int* status, void* stream, const int* q_start = nullptr,
-                                   const int* kv_len = nullptr, int cluster = 1, const int* token_row = nullptr) {
+                                   const int* kv_len = nullptr, int cluster = 1, const int* token_row = nullptr,
+                                   float softcap = 0.f, const float* sink = nullptr) {
+    const ps::SoftmaxExtras extras = ps::softmax_extras(scale, softcap, sink);
     if (T <= 0) return PS_OK;
     if ((q_start == nullptr) != (kv_len == nullptr)) return PS_ERR_BAD_ARGUMENT;
     if (cluster > 1 && (cluster != n_splits || cluster > 8 || (cluster & (cluster - 1)))) return PS_ERR_BAD_ARGUMENT;
@@ -603,7 +607,7 @@ static int launch_attention_decode(const void* q, int q_stride, void* out, int o
                                       (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_stride,
                                       token_item, positions, block_table, bt_stride, n_heads, n_kv_heads, head_dim,
                                       page_size, window, scale * 1.4426950408889634f, chunk_keys, split_chunks,
-                                      n_splits, part_acc, part_ml, counters, status, q_start, kv_len, 1, token_row);
+                                      n_splits, part_acc, part_ml, counters, status, q_start, kv_len, 1, token_row, extras);
     }
 #define PS_DECODE_LAUNCH(KS)                                                                                          \
     {                                                                                                                \
@@ -616,7 +620,7 @@ static int launch_attention_decode(const void* q, int q_stride, void* out, int o
                                       token_item, positions, block_table, bt_stride, n_heads, n_kv_heads, head_dim,   \
                                       page_size, window, scale * 1.4426950408889634f, chunk_keys, split_chunks,       \
                                       n_splits, part_acc, part_ml, counters, status, q_start, kv_len, cluster,        \
-                                      token_row);                                                                     \
+                                      token_row, extras);                                                             \
     }
     if (head_dim <= 64) PS_DECODE_LAUNCH(4)
     if (head_dim <= 128) PS_DECODE_LAUNCH(8)
@@ -653,7 +657,8 @@ PS_EXPORT int ps_paged_attention_decode_checked(const void* q, int q_stride, voi
 // through the scratch arrays. q_start / kv_len (per item, may both be null) tell which keys are older than
 // this step, so that a first chunk of such keys is fetched before the wait on the kernel before.
 // token_row (may be null): the block-table row of each token, where the table is kept by request slot
-// instead of by item.
+// instead of by item. softcap > 0: scores become softcap * tanh(score / softcap); sink (may be null): one
+// float per query head whose exponential joins the softmax's denominator.
 PS_EXPORT int ps_paged_attention_decode_ex(const void* q, int q_stride, void* out, int out_stride,
                                            const void* k_pool, const void* v_pool, long long page_stride,
                                            const int* token_item, const int* token_row, const int* positions,
@@ -662,11 +667,11 @@ PS_EXPORT int ps_paged_attention_decode_ex(const void* q, int q_stride, void* ou
                                            int n_heads, int n_kv_heads, int head_dim, int page_size, int window,
                                            float scale, int split_tiles, int n_splits, int cluster,
                                            float* part_acc, float* part_ml, int* counters, int* status,
-                                           void* stream) {
+                                           float softcap, const float* sink, void* stream) {
     return launch_attention_decode(q, q_stride, out, out_stride, k_pool, v_pool, page_stride, token_item, positions,
                                    block_table, bt_stride, T, n_heads, n_kv_heads, head_dim, page_size, window, scale,
                                    split_tiles, n_splits, part_acc, part_ml, counters, status, stream, q_start, kv_len,
-                                   cluster < 1 ? 1 : cluster, token_row);
+                                   cluster < 1 ? 1 : cluster, token_row, softcap, sink);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -60,7 +60,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
                          const int* __restrict__ q_start, const int* __restrict__ kv_len,
                          const int* __restrict__ block_table, int bt_stride, const int* __restrict__ item_row,
                          int first_item, int n_items, int n_heads, int n_kv_heads, int page_size, int window,
-                         float scale_log2) {
+                         float scale_log2, SoftmaxExtras extras) {
     constexpr int RS = HD + 8;                         // padded row, in elements
     constexpr int CH = HD / 8;                         // 16-byte pieces of a row
     constexpr int KS = HD / 16;                        // k steps over the head dim
@@ -127,6 +127,11 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const int gq = lane >> 2, tq = lane & 3;
+    if (extras.sink && wg == 0) {
+        // the sink starts the state of warp group 0: its four threads of a row share the maximum, one holds the 1
+        m_run[0] = m_run[1] = extras.sink[h] * 1.4426950408889634f;
+        l_run[0] = l_run[1] = tq == 0 ? 1.f : 0.f;
+    }
     const int row0 = warp * 16 + gq, row1 = row0 + 8;            // the two query rows of this thread
     const int pos_r0 = pos0 + row0, pos_r1 = pos0 + row1;
 
@@ -163,7 +168,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
         for (int nt = 0; nt < BKEY / 8; ++nt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                float v = s[nt][e] * scale_log2;
+                float v = score_log2(s[nt][e], scale_log2, extras);
                 if (need_mask) {
                     int key = key0 + nt * 8 + tq * 2 + (e & 1);
                     int pos = (e < 2) ? pos_r0 : pos_r1;
@@ -274,7 +279,7 @@ template <int HD>
 int launch(const void* q, int q_stride, void* out, int out_stride, const void* k_pool, const void* v_pool,
            long long page_stride, const int* q_start, const int* kv_len, const int* block_table, int bt_stride,
            const int* item_row, int first_item, int n_items, int max_blocks, int n_heads, int n_kv_heads,
-           int page_size, int window, float scale, cudaStream_t stream) {
+           int page_size, int window, float scale, float softcap, const float* sink, cudaStream_t stream) {
     constexpr int RS = HD + 8;
     size_t smem = (size_t)(BQ + 8 * BKEY) * RS * 2;
     auto kernel = prefill_attention_kernel<HD>;
@@ -283,7 +288,7 @@ int launch(const void* q, int q_stride, void* out, int out_stride, const void* k
     return launch_pdl(kernel, dim3(max_blocks, n_heads), dim3(THREADS), smem, stream, (const __nv_bfloat16*)q, q_stride,
                       (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
                       page_stride, q_start, kv_len, block_table, bt_stride, item_row, first_item, n_items, n_heads,
-                      n_kv_heads, page_size, window, scale * 1.4426950408889634f);
+                      n_kv_heads, page_size, window, scale * 1.4426950408889634f, softmax_extras(scale, softcap, sink));
 }
 
 }  // namespace pf
@@ -293,12 +298,14 @@ int launch(const void* q, int q_stride, void* out, int out_stride, const void* k
 // i's first token, kv_len[i] its length after the step. max_blocks >= sum over items of ceil(q_len / 64).
 // q and out point at row 0 of the step's flat token arrays. Head sizes: multiples of 16 up to 128.
 // item_row (may be null): the block-table row of each item, where the table is kept by request slot.
+// softcap > 0: scores become softcap * tanh(score / softcap); sink (may be null): one float per query head whose
+// exponential joins the softmax's denominator.
 PS_EXPORT int ps_prefill_attention(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
                                    const void* v_pool, long long page_stride, const int* q_start, const int* kv_len,
                                    const int* block_table, int bt_stride, const int* item_row, int first_item,
                                    int n_items,
                                    int max_blocks, int n_heads, int n_kv_heads, int head_dim, int page_size,
-                                   int window, float scale, void* stream) {
+                                   int window, float scale, float softcap, const float* sink, void* stream) {
     if (n_items <= 0 || max_blocks <= 0) return PS_OK;
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads != 0 || n_heads > 65535) return PS_ERR_BAD_ARGUMENT;
     if (head_dim <= 0 || head_dim % 16 != 0 || head_dim > 128) return PS_ERR_UNSUPPORTED;
@@ -311,7 +318,7 @@ PS_EXPORT int ps_prefill_attention(const void* q, int q_stride, void* out, int o
     case D:                                                                                                        \
         return ps::pf::launch<D>(q, q_stride, out, out_stride, k_pool, v_pool, page_stride, q_start, kv_len,       \
                                  block_table, bt_stride, item_row, first_item, n_items, max_blocks, n_heads,       \
-                                 n_kv_heads, page_size, window, scale, s);
+                                 n_kv_heads, page_size, window, scale, softcap, sink, s);
     switch (head_dim) {
         PS_PF_CASE(16) PS_PF_CASE(32) PS_PF_CASE(48) PS_PF_CASE(64)
         PS_PF_CASE(80) PS_PF_CASE(96) PS_PF_CASE(112) PS_PF_CASE(128)

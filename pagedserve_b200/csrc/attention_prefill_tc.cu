@@ -193,7 +193,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ item_row, int first_item, int n_items, int n_heads,
                             int n_kv_heads, int page_size, int window,
                             float scale_log2, long long k_row_base, long long v_row_base, long long page_rows,
-                            int* __restrict__ status) {
+                            int* __restrict__ status, SoftmaxExtras extras) {
     using L = Layout<HD, SPLIT>;
     constexpr int ROW_THREADS = L::ROW_THREADS, THREADS = L::THREADS, COLS = L::COLS;
     extern __shared__ unsigned char smem_raw[];
@@ -343,6 +343,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
         constexpr int OCOLS = HD / SPLIT;                         // columns of O that this thread owns
         float m_run = -INFINITY, l_run = 0.f;                     // l_run: the sum over this thread's keys only
+        if (extras.sink) {
+            // the sink starts the row's state: both threads of a row share the maximum, the first holds the 1
+            m_run = extras.sink[h] * 1.4426950408889634f;
+            l_run = half == 0 ? 1.f : 0.f;
+        }
+        // capped scores are brought to their final units first and then take the place of the raw ones
+        const float unit_scale = extras.cap_log2 > 0.f ? 1.0f : scale_log2;
         bool ok = true;
         uint32_t it = 0;
         for (int kb = kb_first; kb <= kb_last && ok; ++kb, ++it) {
@@ -354,6 +361,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             tmem_ld_cols<COLS>(lane_base + L::S_COL + col0, sr);
             tc_fence_before();
             mbar_arrive(s_free);                                  // the next tile's scores may overwrite S
+            if (extras.cap_log2 > 0.f) {
+#pragma unroll
+                for (int j = 0; j < COLS; ++j)
+                    sr[j] = __float_as_uint(extras.cap_log2 * tanh_ex2(__uint_as_float(sr[j]) * extras.scale_over_cap));
+            }
             const bool need_mask = (key0 + COLS - 1 > pos0) || (window > 0 && key0 < pos0 + rows - window) || rows < BQ;
             if (need_mask) {
                 // keys this row may see: [max(lo_row, lo), pos]; everything else becomes -inf
@@ -385,7 +397,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 }
                 mx = fmaxf(mx, mx_other);
             }
-            mx *= scale_log2;
+            mx *= unit_scale;
             const float m_new = fmaxf(m_run, mx);
             const float base_m = (m_new == -INFINITY) ? 0.f : m_new;
             const float corr = ex2(m_run - base_m);
@@ -398,10 +410,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 uint32_t pr[32];
 #pragma unroll
                 for (int j = 0; j < 64; j += 4) {
-                    const float p0 = ex2(fmaf(__uint_as_float(sr[c + j]), scale_log2, neg_m));
-                    const float p1 = ex2(fmaf(__uint_as_float(sr[c + j + 1]), scale_log2, neg_m));
-                    const float p2 = ex2(fmaf(__uint_as_float(sr[c + j + 2]), scale_log2, neg_m));
-                    const float p3 = ex2(fmaf(__uint_as_float(sr[c + j + 3]), scale_log2, neg_m));
+                    const float p0 = ex2(fmaf(__uint_as_float(sr[c + j]), unit_scale, neg_m));
+                    const float p1 = ex2(fmaf(__uint_as_float(sr[c + j + 1]), unit_scale, neg_m));
+                    const float p2 = ex2(fmaf(__uint_as_float(sr[c + j + 2]), unit_scale, neg_m));
+                    const float p3 = ex2(fmaf(__uint_as_float(sr[c + j + 3]), unit_scale, neg_m));
                     sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
                     __nv_bfloat162 lo2 = __floats2bfloat162_rn(p0, p1), hi2 = __floats2bfloat162_rn(p2, p3);
                     pr[j >> 1] = *reinterpret_cast<uint32_t*>(&lo2);
@@ -523,7 +535,8 @@ template <int HD, int SPLIT>
 int launch(const void* q, int q_stride, int T, void* out, int out_stride, const void* pool, long long pool_rows,
            long long k_row_base, long long v_row_base, long long page_rows, const int* q_start, const int* kv_len,
            const int* block_table, int bt_stride, const int* item_row, int first_item, int n_items, int max_blocks,
-           int n_heads, int n_kv_heads, int page_size, int window, float scale, int* status, cudaStream_t stream) {
+           int n_heads, int n_kv_heads, int page_size, int window, float scale, int* status, float softcap,
+           const float* sink, cudaStream_t stream) {
     CUtensorMap map_q, map_kv;
     if (!make_map(&map_q, q, T, n_heads * HD, q_stride, BQ)) return PS_ERR_LAUNCH;
     if (!make_map(&map_kv, pool, pool_rows, HD, HD, page_size)) return PS_ERR_LAUNCH;
@@ -535,7 +548,7 @@ int launch(const void* q, int q_stride, int T, void* out, int out_stride, const 
     return launch_pdl(kernel, dim3(n_heads, max_blocks), dim3(L::THREADS), L::SMEM, stream, map_q, map_kv,
                       (__nv_bfloat16*)out, out_stride, q_start, kv_len, block_table, bt_stride, item_row, first_item,
                       n_items, n_heads, n_kv_heads, page_size, window, scale * 1.4426950408889634f, k_row_base,
-                      v_row_base, page_rows, status);
+                      v_row_base, page_rows, status, softmax_extras(scale, softcap, sink));
 }
 
 }  // namespace pftc
@@ -547,13 +560,16 @@ int launch(const void* q, int q_stride, int T, void* out, int out_stride, const 
 // max_blocks >= sum over the items of ceil(q_len / 128). Head sizes 64 and 128, pages of 8..64 tokens.
 // row_threads: threads per query row, 1 or 2 (0: chosen here).
 // item_row (may be null): the block-table row of each item, where the table is kept by request slot.
+// softcap > 0: scores become softcap * tanh(score / softcap); sink (may be null): one float per query head whose
+// exponential joins the softmax's denominator.
 PS_EXPORT int ps_prefill_attention_tc(const void* q, int q_stride, int T, void* out, int out_stride, const void* pool,
                                       long long pool_rows, long long k_row_base, long long v_row_base,
                                       long long page_rows, const int* q_start, const int* kv_len,
                                       const int* block_table, int bt_stride, const int* item_row, int first_item,
                                       int n_items,
                                       int max_blocks, int n_heads, int n_kv_heads, int head_dim, int page_size,
-                                      int window, float scale, int row_threads, int* status, void* stream) {
+                                      int window, float scale, int row_threads, int* status, float softcap,
+                                      const float* sink, void* stream) {
     if (n_items <= 0 || max_blocks <= 0) return PS_OK;
     if (row_threads < 0 || row_threads > 2) return PS_ERR_BAD_ARGUMENT;
     if (!status) return PS_ERR_BAD_ARGUMENT;
@@ -572,7 +588,8 @@ PS_EXPORT int ps_prefill_attention_tc(const void* q, int q_stride, int T, void* 
 #define PS_PFTC_LAUNCH(HD, SPLIT)                                                                                     \
     return ps::pftc::launch<HD, SPLIT>(q, q_stride, T, out, out_stride, pool, pool_rows, k_row_base, v_row_base,     \
                                        page_rows, q_start, kv_len, block_table, bt_stride, item_row, first_item,      \
-                                       n_items, max_blocks, n_heads, n_kv_heads, page_size, window, scale, status, s)
+                                       n_items, max_blocks, n_heads, n_kv_heads, page_size, window, scale, status,    \
+                                       softcap, sink, s)
     if (head_dim == 64) {
         if (two) PS_PFTC_LAUNCH(64, 2);
         PS_PFTC_LAUNCH(64, 1);

@@ -77,6 +77,36 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// Extras of the attention softmax, in the units the tensor-core kernels work in (scores times log2 e):
+//   cap_log2 > 0: the score becomes cap_log2 * tanh(raw * scale_over_cap), with cap_log2 = cap * log2 e and
+//                 scale_over_cap = scale / cap, instead of raw * scale * log2 e;
+//   sink:         one float per query head (natural units) whose exponential joins the denominator. A kernel
+//                 gives it to exactly one of the partial softmax states of a row as that state's start:
+//                 (max, sum) = (sink * log2 e, 1) instead of (-inf, 0), which is a key without a value.
+struct SoftmaxExtras {
+    float cap_log2;
+    float scale_over_cap;
+    const float* sink;
+};
+__host__ __device__ inline SoftmaxExtras softmax_extras(float scale, float softcap, const float* sink) {
+    SoftmaxExtras e;
+    e.cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+    e.scale_over_cap = softcap > 0.f ? scale / softcap : 0.f;
+    e.sink = sink;
+    return e;
+}
+// tanh from one ex2 and one reciprocal: 1 - 2 / (1 + e^(2x)); absolute error about 1e-7, exact at both ends
+__device__ __forceinline__ float tanh_ex2(float x) {
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 2.8853900817779268f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return fmaf(-2.0f, r, 1.0f);
+}
+// a raw q.k product in log2 units, capped or not
+__device__ __forceinline__ float score_log2(float raw, float scale_log2, const SoftmaxExtras& x) {
+    return x.cap_log2 > 0.f ? x.cap_log2 * tanh_ex2(raw * x.scale_over_cap) : raw * scale_log2;
+}
+
 // Where the key and value columns of a packed q|k|v projection go when the product's own epilogue writes them
 // into the pages (k_pool null = nowhere: everything goes to the output buffer).
 struct KvScatter {

@@ -99,9 +99,9 @@ _SIGNATURES = {
         "ps_paged_attention_decode_checked": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
                                               _F, _I, _I, _P, _P, _P, _P, _P],
         "ps_paged_attention_decode_ex": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I,
-                                         _I, _I, _F, _I, _I, _I, _P, _P, _P, _P, _P],
+                                         _I, _I, _F, _I, _I, _I, _P, _P, _P, _P, _F, _P, _P],
         "ps_prefill_attention": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F,
-                                 _P],
+                                 _F, _P, _P],
     },
     "tc": {
         "ps_gemm_tc": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P],
@@ -109,7 +109,7 @@ _SIGNATURES = {
                             _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "ps_gemm_tc_qkv": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "ps_prefill_attention_tc": [_P, _I, _I, _P, _I, _P, _L, _L, _L, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I,
-                                    _I, _I, _F, _I, _P, _P],
+                                    _I, _I, _F, _I, _P, _F, _P, _P],
     },
 }
 
@@ -586,7 +586,7 @@ class Ops:
     def paged_attention_decode(self, q, out, k_pool, v_pool, page_stride, token_item, positions, block_table,
                                n_heads, n_kv_heads, head_dim, page_size, window, scale, max_kv_len,
                                target_ctas=1184, status=None, q_start=None, kv_len=None, merge="global",
-                               largest_cluster=8, token_row=None):
+                               largest_cluster=8, token_row=None, softcap=None, sink=None):
         """Split-key attention for few query tokens (bfloat16).  ``max_kv_len`` bounds the context of
         every token in the call; it fixes the grid, so a CUDA graph passes the model's maximum.
         ``q_start`` / ``kv_len`` (the step's per-item arrays) let the kernel fetch keys older than this step
@@ -594,7 +594,7 @@ class Ops:
         merge through scratch in global memory) or "cluster" (they are a thread-block cluster and merge
         through shared memory; falls back to "global" where more than ``largest_cluster`` splits pay).
         ``block_table`` rows are indexed by ``token_row[t]`` (a table kept by request slot) or, without it, by
-        ``token_item[t]``."""
+        ``token_item[t]``.  ``softcap`` / ``sink`` as in :meth:`paged_attention_simt`."""
         T = q.shape[0]
         _require(q, "q", torch.bfloat16)
         _require(out, "out", torch.bfloat16)
@@ -622,12 +622,13 @@ class Ops:
             page_stride, _ptr(token_item), _ptr(token_row), _ptr(positions), _ptr(block_table),
             block_table.stride(0), _ptr(q_start), _ptr(kv_len), T, n_heads, n_kv_heads, head_dim,
             page_size, window or 0, scale, split_tiles, n_splits, cluster,
-            _ptr(part_acc), _ptr(part_ml), _ptr(counters), _ptr(status), _stream()), "paged_attention_decode")
+            _ptr(part_acc), _ptr(part_ml), _ptr(counters), _ptr(status), float(softcap or 0.0), _ptr(sink),
+            _stream()), "paged_attention_decode")
         return out
 
     def prefill_attention(self, q, out, k_pool, v_pool, page_stride, q_start, kv_len, block_table, first_item,
                           n_items, max_blocks, n_heads, n_kv_heads, head_dim, page_size, window, scale,
-                          item_row=None):
+                          item_row=None, softcap=None, sink=None):
         """Tensor-core causal attention of prompt portions (bfloat16): items ``first_item ..`` of the step,
         ``max_blocks`` >= the number of 64-query blocks they make up.  ``q`` / ``out`` are the step's flat
         token arrays (row 0 = token 0).  ``item_row``: the block-table row of each item (a table kept by request
@@ -641,7 +642,7 @@ class Ops:
             _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pool), _ptr(v_pool),
             page_stride, _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.stride(0), _ptr(item_row),
             first_item, n_items, max_blocks, n_heads, n_kv_heads,
-            head_dim, page_size, window or 0, scale, _stream()),
+            head_dim, page_size, window or 0, scale, float(softcap or 0.0), _ptr(sink), _stream()),
             "prefill_attention")
         return out
 
@@ -652,7 +653,7 @@ class Ops:
 
     def prefill_attention_tc(self, q, out, pool, cache_layer_local, q_start, kv_len, block_table, first_item,
                              n_items, max_blocks, n_heads, n_kv_heads, head_dim, page_size, window, scale,
-                             status=None, row_threads=0, item_row=None):
+                             status=None, row_threads=0, item_row=None, softcap=None, sink=None):
         """tcgen05 causal attention of prompt portions (bfloat16, head size 64 or 128).  ``pool`` is the cache
         group's whole pool ``[pages, layers, 2, kv heads, page size, head dim]``; ``cache_layer_local`` the
         layer's index inside it; ``max_blocks`` >= the number of 128-query blocks of the items.
@@ -672,7 +673,7 @@ class Ops:
             (cache_layer_local * 2) * rows_per_tensor, (cache_layer_local * 2 + 1) * rows_per_tensor, page_rows,
             _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.stride(0), _ptr(item_row), first_item,
             n_items, max_blocks, n_heads, n_kv_heads, head_dim, page_size, window or 0, scale, row_threads,
-            _ptr(status), _stream()),
+            _ptr(status), float(softcap or 0.0), _ptr(sink), _stream()),
             "prefill_attention_tc")
         return out
 
@@ -685,7 +686,7 @@ class Ops:
                            layer.page_stride, n_kv_heads, head_dim, layer.page_size)
         from pagedserve_b200.kernels import tensorcore
 
-        if self.dtype == torch.float32 or head_dim % 16 != 0 or not tensorcore.attention_ok(softcap, sink):
+        if self.dtype == torch.float32 or head_dim % 16 != 0:
             # the CUDA-core kernel takes every head size; the tensor-core kernels want multiples of 16
             return self.paged_attention_simt(q, out, layer.k_pool, layer.v_pool, layer.page_stride,
                                              ctx.token_slot, ctx.positions, layer.block_table, n_heads,

@@ -51,15 +51,11 @@ def linear(ops, a, w, bias, out, act=None, accumulate=False, status=None):
     return ops.linear_simt(a, w, bias, out, act, accumulate)
 
 
-def attention_ok(softcap, sink) -> bool:
-    """Whether the tensor-core attention kernels compute this form of the softmax."""
-    return not softcap and sink is None
-
-
 def attention(ops, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, scale, softcap=None, sink=None):
     """Short entries (fewer than ``ctx.LONG_ENTRY`` tokens: decode tokens, short portions) come first in the
     step's flat batch and go token by token through the split-key kernel; long portions go through the
-    tensor-core prefill kernel in blocks of 64 queries."""
+    tensor-core prefill kernel in blocks of 64 queries.  ``softcap``: scores become softcap * tanh(score /
+    softcap); ``sink``: float32 [n_heads], exp(sink[h]) joins the softmax's denominator of head h."""
     short_tokens = ctx.num_short_tokens
     long_items = ctx.num_items - ctx.num_short_items
     if long_items and head_dim > 128:
@@ -75,7 +71,7 @@ def attention(ops, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, sc
                                    layer.page_stride, ctx.token_item[:short_tokens], ctx.positions[:short_tokens],
                                    layer.block_table, n_heads, n_kv_heads, head_dim, layer.page_size, window, scale,
                                    ctx.max_kv_len, status=ctx.status, q_start=ctx.q_start, kv_len=ctx.kv_len, merge=merge,
-                                   token_row=ctx.token_slot[:short_tokens])
+                                   token_row=ctx.token_slot[:short_tokens], softcap=softcap, sink=sink)
     if long_items:
         if ops.prefill_tc_ok(head_dim, layer.page_size, q, out, getattr(layer, "pool", None)):
             # blocks of 128 queries: never more than the count of 64-query blocks
@@ -86,9 +82,10 @@ def attention(ops, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, sc
             ops.prefill_attention_tc(q, out, layer.pool, layer.pool_layer, ctx.q_start, ctx.kv_len, layer.block_table,
                                      ctx.num_short_items, long_items, ctx.num_long_blocks, n_heads, n_kv_heads,
                                      head_dim, layer.page_size, window, scale, status=ctx.status,
-                                     row_threads=2 if two else 1, item_row=ctx.item_slot)
+                                     row_threads=2 if two else 1, item_row=ctx.item_slot, softcap=softcap, sink=sink)
         else:
             ops.prefill_attention(q, out, layer.k_pool, layer.v_pool, layer.page_stride, ctx.q_start, ctx.kv_len,
                                   layer.block_table, ctx.num_short_items, long_items, ctx.num_long_blocks, n_heads,
-                                  n_kv_heads, head_dim, layer.page_size, window, scale, item_row=ctx.item_slot)
+                                  n_kv_heads, head_dim, layer.page_size, window, scale, item_row=ctx.item_slot,
+                                  softcap=softcap, sink=sink)
     return out

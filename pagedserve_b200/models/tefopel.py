@@ -55,7 +55,7 @@ def build_tefopel_spec(config: TefopelConfig) -> ModelSpec:
         else:
             mixer_spec = PartSpec("wkv", dict(
                 hidden_size=width, n_heads=mixer["heads"], head_dim=mixer["dim"], eps=config.norm_eps,
-                decay_rank=config.random_decay_rank, init_std=width_std,
+                decay_rank=None, random_decay_rank=config.random_decay_rank, init_std=width_std,
                 out_init_std=(mixer["heads"] * mixer["dim"]) ** -0.5), prefix + "mix.")
         norms = {"pre_mixer": PartSpec("layernorm", dict(norm, name="norm1"), prefix)}
         if entry["mlp"] is not None:

@@ -33,7 +33,8 @@ class WkvMixer(Mixer):
     decay's argument leave their products as float32 too.
 
     params: hidden_size, n_heads, head_dim, eps, decay_rank (inner size of W_w1 / W_w2; None: whatever the
-    file holds), names of the tensors (defaults: mu.r ... mu.w, r, k, v, g, w1, w2, w0, u, norm, o).
+    file holds), random_decay_rank (the size random weights are drawn with where decay_rank is None);
+    the tensors are mu.r ... mu.w, r, k, v, g, w1, w2, w0, u, norm, o.
     """
 
     graph_safe = True
@@ -53,12 +54,13 @@ class WkvMixer(Mixer):
     def param_specs(self):
         p = self.params
         W, inner, rank = self.width, self.inner, p.get("decay_rank")
+        drawn = p.get("random_decay_rank", 16) if rank is None else rank
         rank = -1 if rank is None else rank
         std = p.get("init_std", 0.02)
         specs = [(ParamSpec(self._n("mu." + s), (W,), "vector"), ("normal", 0.3)) for s in MIXES]
         specs += [(ParamSpec(self._n(s), (inner, W), "matmul"), ("normal", std)) for s in ("r", "k", "v", "g")]
-        specs += [(ParamSpec(self._n("w1"), (rank, W), "matmul"), ("normal", std)),
-                  (ParamSpec(self._n("w2"), (inner, rank), "matmul"), ("normal", 0.1)),
+        specs += [(ParamSpec(self._n("w1"), (rank, W), "matmul"), ("normal", std, (drawn, W))),
+                  (ParamSpec(self._n("w2"), (inner, rank), "matmul"), ("normal", 0.1, (inner, drawn))),
                   (ParamSpec(self._n("w0"), (inner,), "vector"), ("normal", 1.0)),
                   (ParamSpec(self._n("u"), (p["n_heads"], p["head_dim"]), "vector"), ("normal", 0.3)),
                   (ParamSpec(self._n("norm"), (inner,), "vector"), ("ones_plus_normal", 0.1)),

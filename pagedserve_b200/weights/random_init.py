@@ -36,12 +36,16 @@ def random_tensors(config: ModelConfig, seed: int, storage_dtype: str = "bfloat1
     generator = torch.Generator(device="cpu")
     generator.manual_seed(int(seed))
     tensors: Dict[str, torch.Tensor] = {}
-    for param, (kind, scale) in init_plan(spec):
+    for param, (kind, scale, *drawn_shape) in init_plan(spec):
         if kind == "skip":
             continue
         if param.role == "index":
             raise ValueError("random integer tables are not defined")
-        noise = torch.randn(param.shape, generator=generator, dtype=torch.float32) * scale
+        # a tensor with an extent that only a file gives (-1 in its shape) names the shape to draw as a third item
+        shape = tuple(drawn_shape[0]) if drawn_shape else tuple(param.shape)
+        if any(extent < 0 for extent in shape):
+            raise ValueError(f"{param.name}: no size to draw a free extent with")
+        noise = torch.randn(shape, generator=generator, dtype=torch.float32) * scale
         if kind == "ones_plus_normal":
             noise = noise + 1.0
         elif kind != "normal":

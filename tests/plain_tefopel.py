@@ -24,10 +24,6 @@ def offset_rms_norm(x, w, eps):
     return rms_unit(x, eps) * (1.0 + w)
 
 
-def gelu_tanh(z):
-    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 def rotate_interleaved(x, positions, dims, base):
     """x [T, heads, d]: the neighbours (2i, 2i+1), i < dims/2, turn by p * base^(-2i/dims); the rest stays."""
     i = torch.arange(dims // 2, dtype=x.dtype)
