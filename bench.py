@@ -300,6 +300,129 @@ def _run_reference(args, ref):
     return result
 
 
+# ---------------------------------------------------------------------------------------------------------
+# --design tefopel: the design's prefill and decode throughput beside GPT-2 of equal size, and its kernels alone
+DESIGN_SIZES = {
+    # name: width, heads, head size, inner size, layers, wkv heads (of size 64), window
+    "w1024": dict(width=1024, heads=16, head_dim=64, ff=4096, layers=8, wkv_heads=16, window=1024),
+    "w2048": dict(width=2048, heads=16, head_dim=128, ff=8192, layers=8, wkv_heads=32, window=1024),
+}
+DESIGN_VOCAB, DESIGN_CONTEXT = 32000, 2048
+
+
+def design_arm(args):
+    """Random models at sizes that resemble real layers: Tefopel (three attention layers, then one wkv layer,
+    repeated) and GPT-2 with the same width, depth, heads, inner size and vocabulary.  Per model: tokens/s of a
+    2,048-token prefill step (two prompts of 1,024) and of decode steps at batch 8 and 64 over 512-token
+    prompts.  Then the design's kernels alone beside the like kernels of GPT-2, against the measured peaks."""
+    import numpy as np
+    import torch
+
+    from pagedserve_b200.config.engine_config import EngineConfig
+    from pagedserve_b200.config.gpt2 import GPT2Config
+    from pagedserve_b200.config.tefopel import TefopelConfig, attention_layer, wkv_layer
+    from pagedserve_b200.engine.batch import StepEntry
+    from pagedserve_b200.engine.engine import Engine
+    from pagedserve_b200.kernels import microbench
+
+    peaks = load_peaks()
+    rng = np.random.default_rng(0)
+    steps, warmup = min(args.steps, 64), max(args.warmup, 3)
+
+    def configs(size):
+        layers = []
+        for index in range(size["layers"]):
+            if index % 4 == 3:
+                layers.append(wkv_layer(size["wkv_heads"], 64, ff=size["ff"]))
+            else:
+                layers.append(attention_layer(size["heads"], size["heads"], size["head_dim"], size["window"],
+                                              size["ff"], rot_dims=size["head_dim"] // 2))
+        tefopel = TefopelConfig(vocab=DESIGN_VOCAB, width=size["width"], norm_eps=1e-5, layers=layers)
+        gpt2 = GPT2Config(n_layer=size["layers"], n_embd=size["width"], n_head=size["heads"], n_inner=size["ff"],
+                          vocab_size=DESIGN_VOCAB, n_positions=DESIGN_CONTEXT)
+        return {"tefopel": tefopel, "gpt2": gpt2}
+
+    def timed(fn):
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        out = fn()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end), out
+
+    def measure(config):
+        pages = 64 * (DESIGN_CONTEXT // 16) + 64
+        engine = Engine.random(config, 0, EngineConfig(dtype=args.dtype, block_size=16, num_blocks=pages,
+                                                       max_num_seqs=64, max_num_batched_tokens=2048,
+                                                       max_model_len=DESIGN_CONTEXT))
+        vocab = config.vocabulary_size
+        result = {"weights_mb": engine.model.weight_bytes() / 1e6}
+        # prefill: two prompts of 1,024 in one step; the shape is captured as a CUDA graph after a few sightings
+        rehearsals = max(3, getattr(engine.runner, "MIXED_SHAPE_SIGHTINGS", 2) + 1)
+        times = []
+        for repeat in range(rehearsals + 5):
+            entries = [StepEntry(1000 + i, rng.integers(0, vocab, 1024).tolist(), [1023]) for i in range(2)]
+            ms, _ = timed(lambda: engine.step(entries))
+            if repeat >= rehearsals:
+                times.append(ms)
+            for i in range(2):
+                engine.finish(1000 + i)
+        result["prefill_tok_s"] = 2048 / (statistics.median(times) / 1e3)
+        result["prefill_ms"] = statistics.median(times)
+        for batch in (8, 64):
+            tokens = []
+            for first in range(0, batch, 4):
+                group = range(first, min(batch, first + 4))
+                logits = engine.step([StepEntry(i, rng.integers(0, vocab, 512).tolist(), [511]) for i in group])
+                tokens += logits.argmax(-1).tolist()
+            entries = [StepEntry(i, [tokens[i]]) for i in range(batch)]
+            warm = engine.decode(entries, [0.0] * batch, [0] * batch, steps=warmup)
+            entries = [StepEntry(i, [int(warm[-1, i])]) for i in range(batch)]
+            with ClockSampler() as clocks:
+                ms, out = timed(lambda: engine.decode(entries, [0.0] * batch, [0] * batch, steps=steps))
+            assert out.shape == (steps, batch)
+            for i in range(batch):
+                engine.finish(i)
+            result[f"decode_b{batch}_tok_s"] = batch * steps / (ms / 1e3)
+            result[f"decode_b{batch}_ms_per_step"] = ms / steps
+            result[f"decode_b{batch}_clocks"] = clocks.summary()
+        engine.check_status()
+        del engine
+        torch.cuda.empty_cache()
+        return result
+
+    report = {"impl": "ours", "design": args.design, "dtype": args.dtype, "data": "synthetic (random weights, uniform ids)",
+              "steps": steps, "warmup": warmup, "peaks": peaks, "models": {}, "kernels": {}}
+    for name in (args.design_sizes.split(",") if args.design_sizes else DESIGN_SIZES):
+        size = DESIGN_SIZES[name]
+        report["models"][name] = {"size": size, **{kind: measure(config) for kind, config in configs(size).items()}}
+        both = report["models"][name]
+        both["tefopel_over_gpt2"] = {key: both["tefopel"][key] / both["gpt2"][key]
+                                     for key in ("prefill_tok_s", "decode_b8_tok_s", "decode_b64_tok_s")}
+    if args.dtype == "bfloat16" and not args.skip_points:
+        hbm, tensor = peaks["hbm_gbs"], peaks["bf16_tflops"]
+        kernels = report["kernels"]
+        for hd in (64, 128):
+            plain = microbench.time_decode_attention(64, 1024, 16, 16, hd)
+            full = microbench.time_decode_attention(64, 1024, 16, 16, hd, window=1024, softcap=50.0, sink=True)
+            kernels[f"decode_attention_hd{hd}"] = {
+                "gpt2": {**plain, "frac_hbm": plain["gbs"] / hbm}, "tefopel": {**full, "frac_hbm": full["gbs"] / hbm}}
+            plain = microbench.time_prefill_attention(2, 1024, 16, 16, hd)
+            full = microbench.time_prefill_attention(2, 1024, 16, 16, hd, window=1024, softcap=50.0, sink=True)
+            kernels[f"prefill_attention_hd{hd}"] = {
+                "gpt2": {**plain, "frac_tensor": plain["tflops"] / tensor},
+                "tefopel": {**full, "frac_tensor": full["tflops"] / tensor}}
+        write = microbench.time_cache_write(2048, 16, 16, 64)
+        kernels["cache_write_2048_tokens"] = {**write, "frac_hbm": write["gbs"] / hbm,
+                                              "plain_write_frac_hbm": write["plain_write_gbs"] / hbm}
+        for label, items, each in (("prefill_2x1024", 2, 1024), ("decode_b64", 64, 1), ("decode_b8", 8, 1)):
+            run = microbench.time_wkv(items, each, 16, 64, 1024)
+            kernels[f"wkv_{label}"] = {**run, "frac_hbm": run["gbs"] / hbm}
+    print(json.dumps(report))
+    return 0
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -320,6 +443,10 @@ def main():
     parser.add_argument("--serving", type=int, default=0, metavar="REQUESTS",
                         help="instead of the decode measurement: this many requests (prompts U[64,1024), outputs "
                              "U[32,256]) through the scheduler, chunked prefill under a 2,048-token budget")
+    parser.add_argument("--design", default=None, choices=("tefopel",),
+                        help="instead of the default workload: prefill and decode throughput of this design at a few "
+                             "sizes beside GPT-2 of equal size, and its kernels alone against the measured peaks")
+    parser.add_argument("--design-sizes", default=None, help="comma-separated names out of: " + ", ".join(DESIGN_SIZES))
     args = parser.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -330,6 +457,8 @@ def main():
         return 2
     if args.impl == "reference":
         return reference_arm(args)
+    if args.design:
+        return design_arm(args)
 
     import numpy as np
     import torch

@@ -66,6 +66,27 @@ __device__ __forceinline__ float apply_act(float x, int act) {
     return x;
 }
 
+// the same over a thread's block of values, with the choice made once outside the loop
+template <int N>
+__device__ __forceinline__ void apply_act_all(float (&v)[N], int act) {
+    if (act == PS_ACT_RELU_SQUARED) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) v[j] = relu_squared(v[j]);
+    } else if (act == PS_ACT_SILU) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) v[j] = silu(v[j]);
+    } else if (act == PS_ACT_GELU_TANH) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) v[j] = gelu_tanh(v[j]);
+    } else if (act == PS_ACT_TANH) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) v[j] = tanhf(v[j]);
+    } else if (act == PS_ACT_GELU_ERF) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) v[j] = gelu_erf(v[j]);
+    }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

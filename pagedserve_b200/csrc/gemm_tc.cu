@@ -317,8 +317,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                             for (int j = 0; j < 32; ++j) v[j] = sizeof(TOut) == 2 ? gelu_tanh_fast(v[j]) : gelu_tanh(v[j]);
                         } else if (act != PS_ACT_NONE) {
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], act);
+                            apply_act_all(v, act);
                         }
                         // 16-byte pieces of the row, XOR-swizzled by the row as the tensor map expects
                         if constexpr (sizeof(TOut) == 2) {
@@ -401,10 +400,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                 if (n + j < N) v[j] += bias[n + j];
                         }
                     }
-                    if (act != PS_ACT_NONE) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], act);
-                    }
+                    if (act != PS_ACT_NONE) apply_act_all(v, act);
                     if constexpr (sizeof(TOut) == 2) {
                         if (full_chunk && ((((uintptr_t)(orow + n)) & 15) == 0)) {
 #pragma unroll

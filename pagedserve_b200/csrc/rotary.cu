@@ -18,6 +18,8 @@
 
 namespace ps {
 
+constexpr int ROTARY_MAX_PAIRS = 256;                      // turning pairs of a head: head sizes up to 512
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 rotary_cache_write_kernel(T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride,
@@ -39,7 +41,15 @@ rotary_cache_write_kernel(T* __restrict__ q, int q_stride, const T* __restrict__
         const int page = block_table[(size_t)token_row[t] * bt_stride + p / page_size];
         if (page >= 0) page_base = (long long)page * page_stride + (long long)(p % page_size) * head_dim;
     }
+    // a token's sines and cosines are the same for every head: once into shared memory
+    __shared__ float2 turn[ROTARY_MAX_PAIRS];
     const float pos = (float)p;
+    for (int unit = threadIdx.x; unit < half; unit += blockDim.x) {
+        float sn, cs;
+        sincosf(pos * inv_freq[unit], &sn, &cs);
+        turn[unit] = make_float2(cs, sn);
+    }
+    __syncthreads();
     T* q_row = q + (size_t)t * q_stride;
     const T* k_row = k + (size_t)t * k_stride;
     const int total = (n_heads + n_kv_heads) * units;
@@ -57,8 +67,7 @@ rotary_cache_write_kernel(T* __restrict__ q, int q_stride, const T* __restrict__
             continue;
         }
         const int da = interleaved ? 2 * unit : unit, db = interleaved ? 2 * unit + 1 : unit + half;
-        float sn, cs;
-        sincosf(pos * inv_freq[unit], &sn, &cs);
+        const float cs = turn[unit].x, sn = turn[unit].y;
         if (is_query) {
             T* row = q_row + head * head_dim;
             const float a = to_float(row[da]), b = to_float(row[db]);
@@ -96,6 +105,7 @@ PS_EXPORT int ps_rotary_cache_write(void* q, int q_stride, const void* k, int k_
     if (n_heads < 0 || n_kv_heads < 0 || head_dim <= 0 || rot_dims < 0 || rot_dims > head_dim || (rot_dims & 1))
         return PS_ERR_BAD_ARGUMENT;
     if (rot_dims > 0 && !inv_freq) return PS_ERR_BAD_ARGUMENT;
+    if (rot_dims / 2 > ps::ROTARY_MAX_PAIRS) return PS_ERR_UNSUPPORTED;
     if (k_pool && (!v_pool || !token_row || !block_table || page_size <= 0)) return PS_ERR_BAD_ARGUMENT;
     if (!positions || !q || !k) return PS_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;

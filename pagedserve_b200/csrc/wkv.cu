@@ -11,10 +11,12 @@
 // wkv_recurrence:   per (entry, head), tokens in order:
 //                     w_t = exp(-exp(decay_t))                               (float32)
 //                     y_t[j] = sum_i r_t[i] * (S[i][j] + u[i] k_t[i] v_t[j])
+//                            = sum_i r_t[i] S[i][j]  +  v_t[j] * sum_i r_t[i] u[i] k_t[i]
 //                     S[i][j] <- w_t[i] S[i][j] + k_t[i] v_t[j]
 //                   then y_t / sqrt(mean_j y_t[j]^2 + eps) * gain[j] * gate_t[j], rounded to the output type.
-//                   Thread j of a CTA owns column j of S in registers; a token's r, k, w are staged in shared
-//                   memory. Sums run over i in order: a token's result does not depend on what else is in the step.
+//                   One CTA per (entry, head); S lives in registers, a block of rows x 4 columns per thread;
+//                   tokens are brought into shared memory in chunks, one chunk ahead of the one being computed. Sums run in a fixed order: a token's result does not depend on what else is in the
+//                   step, nor on where a prompt was cut.
 //                   r, k, v, decay and gate are float32 whatever the compute type is.
 #include "common.cuh"
 
@@ -45,70 +47,217 @@ token_shift_mix_kernel(const T* __restrict__ x, int x_stride, const float* __res
     }
 }
 
+__device__ __forceinline__ void wkv_copy16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void wkv_copy4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
+                 : "memory");
+}
+
+// Shared memory of one CTA, in floats: two buffers of CH tokens (r, k, w in rows of PARTS runs; v, gate in plain
+// rows), the chunk's unnormalised outputs, its bonus numbers, and the head's u and gain.
+template <int DMAX>
+struct WkvLayout {
+    static constexpr int COLS = 4;                                      // columns of S per thread
+    static constexpr int IQ = DMAX > 64 ? 8 : 4;                        // rows of S per thread
+    static constexpr int PARTS = DMAX / IQ;                             // threads that share a column: 8 or 16
+    static constexpr int RUN = IQ == 4 ? 4 : IQ + 4;                    // a part's run of a row, padded against bank conflicts
+    static constexpr int ROW = PARTS * RUN;
+    static constexpr int CH = 16;                                       // tokens per chunk
+    static constexpr int THREADS = (DMAX / COLS) * PARTS, WARPS = THREADS / 32;
+    static constexpr int BUF = 3 * CH * ROW + 2 * CH * DMAX;
+    static constexpr int Y = 2 * BUF, BONUS = Y + CH * DMAX, U = BONUS + CH, GAIN = U + DMAX, FLOATS = GAIN + DMAX;
+    static constexpr size_t BYTES = (size_t)FLOATS * 4;
+    static_assert(PARTS == 8 || PARTS == 16, "the sum over parts is a butterfly inside a warp");
+};
+
 template <typename T, int DMAX>
-__global__ void __launch_bounds__(DMAX)
+__global__ void __launch_bounds__(WkvLayout<DMAX>::THREADS)
 wkv_recurrence_kernel(const float* __restrict__ r, const float* __restrict__ k, const float* __restrict__ v,
                       const float* __restrict__ decay, const float* __restrict__ gate, int ld,
                       const float* __restrict__ u, const float* __restrict__ gain, float eps,
                       const T* __restrict__ x, int x_stride, int W, float* __restrict__ state, long long state_stride,
                       int prev_offset, const int* __restrict__ q_start, const int* __restrict__ item_slot,
                       T* __restrict__ out, int out_stride, int heads, int d) {
-    __shared__ float s_r[2][DMAX], s_k[2][DMAX], s_w[2][DMAX], s_u[DMAX];
-    __shared__ float red[2][DMAX / 32];
+    // Thread (group, part) holds a block of S in registers: rows part * IQ .. + IQ - 1 of the four columns
+    // 4 * group .. + 3, so that a token's r, k, w, read from shared memory, are used four times each. The PARTS
+    // threads of a group are neighbours in a warp and add their partial sums up with shuffles. Tokens come in
+    // chunks of CH through two buffers (asynchronous copies, one chunk ahead); inside a chunk the warps run
+    // without barriers: the head norm, which needs all columns of a token, runs once per chunk over the outputs
+    // kept in shared memory.
+    using L = WkvLayout<DMAX>;
+    constexpr int IQ = L::IQ, PARTS = L::PARTS, RUN = L::RUN, ROW = L::ROW, CH = L::CH, THREADS = L::THREADS,
+                  WARPS = L::WARPS, Q4 = IQ / 4;
+    extern __shared__ __align__(16) float wkv_smem[];
+    float* const s_y = wkv_smem + L::Y;
+    float* const s_bonus = wkv_smem + L::BONUS;
+    float* const s_u = wkv_smem + L::U;
+    float* const s_gain = wkv_smem + L::GAIN;
+    const int item = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int begin = q_start[item], end = q_start[item + 1];
+    if (begin >= end) return;
+    const int part = tid % PARTS, j0 = (tid / PARTS) * 4, i0 = part * IQ;
+    const int lane = tid & 31, warp = tid >> 5;
+    // channels past d stay zero in both buffers: they add nothing to any sum and keep their (zero) entries of S
+    if (d < DMAX)
+        for (int e = tid; e < 2 * L::BUF; e += THREADS) wkv_smem[e] = 0.f;
+    for (int i = tid; i < DMAX; i += THREADS) {
+        s_u[i] = i < d ? u[h * d + i] : 0.f;
+        s_gain[i] = i < d ? gain[h * d + i] : 0.f;
+    }
+    __syncthreads();
     pdl_prologue();
     r = pdl_fresh(r); k = pdl_fresh(k); v = pdl_fresh(v); decay = pdl_fresh(decay); gate = pdl_fresh(gate);
     x = pdl_fresh(x);
-    const int item = blockIdx.x, h = blockIdx.y, j = threadIdx.x;
-    const int begin = q_start[item], end = q_start[item + 1];
-    if (begin >= end) return;
-    const bool live = j < d;
-    const int lane = j & 31, warp = j >> 5, warps = (d + 31) >> 5;
-    float* row_state = state + (long long)item_slot[item] * state_stride;
-    float* S = row_state + (long long)h * d * d;
-    float col[DMAX];
-#pragma unroll
-    for (int i = 0; i < DMAX; ++i) col[i] = (live && i < d) ? S[(size_t)i * d + j] : 0.f;
-    const int c = h * d + j;
-    s_u[j] = live ? u[c] : 0.f;
-    const float gain_j = live ? gain[c] : 0.f;
-    const float inv_d = 1.0f / (float)d;
-    for (int t = begin; t < end; ++t) {
-        const int b = (t - begin) & 1;
-        const size_t at = (size_t)t * ld + c;
-        float vj = 0.f;
-        if (live) {
-            s_r[b][j] = r[at];
-            s_k[b][j] = k[at];
-            s_w[b][j] = expf(-expf(decay[at]));
-            vj = v[at];
-        }
-        __syncthreads();                      // the token's r, k, w are staged (the other buffer is the token before)
-        float y = 0.f;
-#pragma unroll
-        for (int i = 0; i < DMAX; ++i) {
-            if (i < d) {
-                const float kv = s_k[b][i] * vj;
-                y = fmaf(s_r[b][i], fmaf(s_u[i], kv, col[i]), y);
-                col[i] = fmaf(s_w[b][i], col[i], kv);
+    const bool wide = (d & 3) == 0 && (ld & 3) == 0 &&
+                      ((((uintptr_t)r | (uintptr_t)k | (uintptr_t)v | (uintptr_t)decay | (uintptr_t)gate) & 15) == 0);
+    const int n_chunks = (end - begin + CH - 1) / CH;
+    auto issue = [&](int chunk) {
+        float* buf = wkv_smem + (chunk & 1) * L::BUF;
+        const int t0 = begin + chunk * CH, n = min(CH, end - t0);
+        if (wide) {
+            const int pieces = d >> 2;                                    // 16-byte pieces of a row
+            for (int e = tid; e < n * pieces; e += THREADS) {
+                const int tt = e / pieces, pc = e - tt * pieces, i = pc << 2;
+                const size_t at = (size_t)(t0 + tt) * ld + h * d + i;
+                const int padded = tt * ROW + (i / IQ) * RUN + (i % IQ);
+                wkv_copy16(buf + padded, r + at);
+                wkv_copy16(buf + CH * ROW + padded, k + at);
+                wkv_copy16(buf + 2 * CH * ROW + padded, decay + at);
+                wkv_copy16(buf + 3 * CH * ROW + tt * DMAX + i, v + at);
+                wkv_copy16(buf + 3 * CH * ROW + CH * DMAX + tt * DMAX + i, gate + at);
+            }
+        } else {
+            for (int e = tid; e < n * d; e += THREADS) {
+                const int tt = e / d, i = e - tt * d;
+                const size_t at = (size_t)(t0 + tt) * ld + h * d + i;
+                const int padded = tt * ROW + (i / IQ) * RUN + (i % IQ);
+                wkv_copy4(buf + padded, r + at);
+                wkv_copy4(buf + CH * ROW + padded, k + at);
+                wkv_copy4(buf + 2 * CH * ROW + padded, decay + at);
+                wkv_copy4(buf + 3 * CH * ROW + tt * DMAX + i, v + at);
+                wkv_copy4(buf + 3 * CH * ROW + CH * DMAX + tt * DMAX + i, gate + at);
             }
         }
-        const float sq = warp_sum(live ? y * y : 0.f);
-        if (lane == 0) red[b][warp] = sq;
-        __syncthreads();
-        float total = 0.f;
-        for (int w = 0; w < warps; ++w) total += red[b][w];
-        if (live)
-            out[(size_t)t * out_stride + c] = from_float<T>(y * rsqrtf(total * inv_d + eps) * gain_j * gate[at]);
-    }
-    if (live) {
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    issue(0);
+    float* row_state = state + (long long)item_slot[item] * state_stride;
+    float* S = row_state + (long long)h * d * d;
+    const bool wide_state = (d & 3) == 0 && (((uintptr_t)S) & 15) == 0;
+    float s[IQ][4];                                           // s[ii][c] = S[i0 + ii][j0 + c]
 #pragma unroll
-        for (int i = 0; i < DMAX; ++i)
-            if (i < d) S[(size_t)i * d + j] = col[i];
+    for (int ii = 0; ii < IQ; ++ii) {
+        const int i = i0 + ii;
+        if (wide_state && i < d && j0 < d) {
+            const float4 got = *reinterpret_cast<const float4*>(S + (size_t)i * d + j0);
+            s[ii][0] = got.x; s[ii][1] = got.y; s[ii][2] = got.z; s[ii][3] = got.w;
+        } else {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) s[ii][c] = (i < d && j0 + c < d) ? S[(size_t)i * d + j0 + c] : 0.f;
+        }
+    }
+    // after the butterfly below, a thread holds the sum of column j0 + mine
+    const int mine = 2 * (part & 1) + ((part >> 1) & 1);
+    const float inv_d = 1.0f / (float)d;
+    for (int chunk = 0; chunk < n_chunks; ++chunk) {
+        float* buf = wkv_smem + (chunk & 1) * L::BUF;
+        float* s_r = buf;
+        float* s_k = buf + CH * ROW;
+        float* s_w = buf + 2 * CH * ROW;
+        const float* s_v = buf + 3 * CH * ROW;
+        const float* s_g = s_v + CH * DMAX;
+        const int t0 = begin + chunk * CH, n = min(CH, end - t0);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();                                      // everybody's copies of this chunk have landed, and
+        if (chunk + 1 < n_chunks) issue(chunk + 1);           // nobody reads the other buffer any more
+        // decay arguments become decays, in place; one number per token for the bonus:
+        // y_j gets v_j * sum_i r_i u_i k_i, the part of the sum that the token's own k v^T contributes
+        for (int e = tid; e < n * d; e += THREADS) {
+            const int tt = e / d, i = e - tt * d;
+            const int padded = tt * ROW + (i / IQ) * RUN + (i % IQ);
+            s_w[padded] = expf(-expf(s_w[padded]));
+        }
+        for (int tt = warp; tt < n; tt += WARPS) {
+            float p = 0.f;
+            for (int i = lane; i < d; i += 32) {
+                const int padded = tt * ROW + (i / IQ) * RUN + (i % IQ);
+                p = fmaf(s_r[padded] * s_u[i], s_k[padded], p);
+            }
+            p = warp_sum(p);
+            if (lane == 0) s_bonus[tt] = p;
+        }
+        __syncthreads();
+        // the token's operands are read one token ahead of their use
+        float4 rr[Q4], kk[Q4], ww[Q4], vv;
+        auto load = [&](int tt) {
+#pragma unroll
+            for (int q = 0; q < Q4; ++q) {
+                rr[q] = *reinterpret_cast<const float4*>(s_r + tt * ROW + part * RUN + 4 * q);
+                kk[q] = *reinterpret_cast<const float4*>(s_k + tt * ROW + part * RUN + 4 * q);
+                ww[q] = *reinterpret_cast<const float4*>(s_w + tt * ROW + part * RUN + 4 * q);
+            }
+            vv = *reinterpret_cast<const float4*>(s_v + tt * DMAX + j0);
+        };
+        load(0);
+        for (int tt = 0; tt < n; ++tt) {
+            float ri[IQ], ki[IQ], wi[IQ];
+#pragma unroll
+            for (int q = 0; q < Q4; ++q) {
+                ri[4 * q] = rr[q].x; ri[4 * q + 1] = rr[q].y; ri[4 * q + 2] = rr[q].z; ri[4 * q + 3] = rr[q].w;
+                ki[4 * q] = kk[q].x; ki[4 * q + 1] = kk[q].y; ki[4 * q + 2] = kk[q].z; ki[4 * q + 3] = kk[q].w;
+                wi[4 * q] = ww[q].x; wi[4 * q + 1] = ww[q].y; wi[4 * q + 2] = ww[q].z; wi[4 * q + 3] = ww[q].w;
+            }
+            const float vc[4] = {vv.x, vv.y, vv.z, vv.w};
+            if (tt + 1 < n) load(tt + 1);
+            float y[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ii = 0; ii < IQ; ++ii) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    y[c] = fmaf(ri[ii], s[ii][c], y[c]);
+                    s[ii][c] = fmaf(wi[ii], s[ii][c], ki[ii] * vc[c]);
+                }
+            }
+            // sum over the parts in a fixed order; on the way every thread keeps fewer columns: 4 -> 2 -> 1
+            const bool odd = part & 1, upper = (part >> 1) & 1;
+            const float got0 = __shfl_xor_sync(0xffffffffu, odd ? y[0] : y[2], 1);
+            const float got1 = __shfl_xor_sync(0xffffffffu, odd ? y[1] : y[3], 1);
+            const float a0 = (odd ? y[2] : y[0]) + got0, a1 = (odd ? y[3] : y[1]) + got1;
+            float b = (upper ? a1 : a0) + __shfl_xor_sync(0xffffffffu, upper ? a0 : a1, 2);
+            b += __shfl_xor_sync(0xffffffffu, b, 4);
+            if (PARTS == 16) b += __shfl_xor_sync(0xffffffffu, b, 8);
+            const float v_mine = mine == 0 ? vc[0] : mine == 1 ? vc[1] : mine == 2 ? vc[2] : vc[3];
+            if (part < 4) s_y[tt * DMAX + j0 + mine] = fmaf(v_mine, s_bonus[tt], b);
+        }
+        __syncthreads();
+        // the head norm, the gain and the gate for the chunk's tokens: a warp per token
+        for (int tt = warp; tt < n; tt += WARPS) {
+            float sq = 0.f;
+            for (int i = lane; i < d; i += 32) sq = fmaf(s_y[tt * DMAX + i], s_y[tt * DMAX + i], sq);
+            const float scale = rsqrtf(warp_sum(sq) * inv_d + eps);
+            T* row = out + (size_t)(t0 + tt) * out_stride + h * d;
+            for (int i = lane; i < d; i += 32)
+                row[i] = from_float<T>(s_y[tt * DMAX + i] * scale * s_gain[i] * s_g[tt * DMAX + i]);
+        }
+    }
+#pragma unroll
+    for (int ii = 0; ii < IQ; ++ii) {
+        const int i = i0 + ii;
+        if (wide_state && i < d && j0 < d) {
+            *reinterpret_cast<float4*>(S + (size_t)i * d + j0) = make_float4(s[ii][0], s[ii][1], s[ii][2], s[ii][3]);
+        } else {
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                if (i < d && j0 + c < d) S[(size_t)i * d + j0 + c] = s[ii][c];
+        }
     }
     // the entry's newest input becomes `last` (each head's CTA copies a share of the row)
     const T* newest = x + (size_t)(end - 1) * x_stride;
     float* last = row_state + prev_offset;
-    for (int w = h * DMAX + j; w < W; w += heads * DMAX) last[w] = to_float(newest[w]);
+    for (int w = h * THREADS + tid; w < W; w += heads * THREADS) last[w] = to_float(newest[w]);
 }
 
 template <typename T, int DMAX>
@@ -116,8 +265,12 @@ int launch_wkv(const float* r, const float* k, const float* v, const float* deca
                const float* u, const float* gain, float eps, const void* x, int x_stride, int W, float* state,
                long long state_stride, int prev_offset, const int* q_start, const int* item_slot, void* out,
                int out_stride, int n_items, int heads, int d, cudaStream_t s) {
-    return launch_pdl(wkv_recurrence_kernel<T, DMAX>, dim3(n_items, heads), dim3(DMAX), 0, s, r, k, v, decay, gate, ld, u,
-                      gain, eps, (const T*)x, x_stride, W, state, state_stride, prev_offset, q_start, item_slot,
+    using L = WkvLayout<DMAX>;
+    auto kernel = wkv_recurrence_kernel<T, DMAX>;
+    static size_t raised[MAX_DEVICES] = {0};
+    if (!ensure_dynamic_smem((const void*)kernel, L::BYTES, raised)) return PS_ERR_LAUNCH;
+    return launch_pdl(kernel, dim3(n_items, heads), dim3(L::THREADS), L::BYTES, s, r, k, v, decay, gate, ld,
+                      u, gain, eps, (const T*)x, x_stride, W, state, state_stride, prev_offset, q_start, item_slot,
                       (T*)out, out_stride, heads, d);
 }
 
@@ -131,7 +284,6 @@ int pick_wkv(const float* r, const float* k, const float* v, const float* decay,
                              q_start, item_slot, out, out_stride, n_items, heads, d, s)
     if (d <= 32) PS_WKV(32);
     if (d <= 64) PS_WKV(64);
-    if (d <= 96) PS_WKV(96);
     PS_WKV(128);
 #undef PS_WKV
 }

@@ -2,6 +2,7 @@
 
     python -m pagedserve_b200.kernels.microbench gemm --m 2048 --n 2304 --k 768 [--bn 0] [--impl tc|skinny|rows|simt]
     python -m pagedserve_b200.kernels.microbench attention --batch 64 --context 640 [--heads 12 --head-dim 64]
+    python -m pagedserve_b200.kernels.microbench wkv --items 2 --tokens 1024 [--heads 16 --head-dim 64]
 
 ``gemm`` prints achieved TFLOP/s and the bytes-per-second of streaming the weight once;
 ``attention`` prints achieved GB/s over the K and V bytes of the contexts.  Inputs are rotated
@@ -118,6 +119,129 @@ def bench_attention(args):
           f"{nbytes / seconds / 1e9:.0f} GB/s of K+V, status {int(status.item())}")
 
 
+# ------------------------------------------------------------------ kernels as functions (bench.py calls these)
+def _paged_inputs(items, context, kv_heads, head_dim, page, rotate_mb=200):
+    """A pool of random pages with one table row per item; several layers so that repeats miss the L2."""
+    pages_per = -(-context // page)
+    layer_bytes = items * pages_per * page * kv_heads * head_dim * 4
+    layers = max(1, min(16, int(rotate_mb * 1e6 // layer_bytes) + 1))
+    pool = torch.randn(items * pages_per + 1, layers, 2, kv_heads, page, head_dim, device="cuda").to(torch.bfloat16)
+    table = torch.randperm(items * pages_per, device="cuda").to(torch.int32).view(items, pages_per)
+    return pool, table, layers, layers * 2 * kv_heads * page * head_dim
+
+
+def time_decode_attention(batch, context, heads, kv_heads, head_dim, page=16, window=None, softcap=None,
+                          sink=False, iters=20):
+    """One decode token per request over ``context`` keys (bfloat16 split-key kernel); GB/s over the K and V
+    bytes a token may see."""
+    from pagedserve_b200.kernels.ops import Ops
+
+    ops = Ops(torch.bfloat16)
+    pool, table, layers, stride = _paged_inputs(batch, context, kv_heads, head_dim, page)
+    q = torch.randn(batch, heads * head_dim, device="cuda").to(torch.bfloat16)
+    out = torch.empty_like(q)
+    token_item = torch.arange(batch, dtype=torch.int32, device="cuda")
+    positions = torch.full((batch,), context - 1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    sinks = torch.randn(heads, device="cuda") if sink else None
+
+    def run(i):
+        layer = i % layers
+        ops.paged_attention_decode(q, out, pool[:, layer, 0], pool[:, layer, 1], stride, token_item, positions, table,
+                                   heads, kv_heads, head_dim, page, window, head_dim ** -0.5, context, status=status,
+                                   softcap=softcap, sink=sinks)
+
+    seconds = _time(run, iters, graph=True)
+    seen = min(context, window) if window else context
+    nbytes = batch * seen * kv_heads * head_dim * 2 * 2
+    return {"us": seconds * 1e6, "gbs": nbytes / seconds / 1e9, "status": int(status.item())}
+
+
+def time_prefill_attention(prompts, prompt_len, heads, kv_heads, head_dim, page=16, window=None, softcap=None,
+                           sink=False, iters=10):
+    """Whole prompts through the tcgen05 prompt kernel (bfloat16, head size 64 or 128); TFLOP/s over the
+    products of the keys a query may see."""
+    from pagedserve_b200.kernels.ops import Ops
+
+    ops = Ops(torch.bfloat16)
+    pool, table, layers, _ = _paged_inputs(prompts, prompt_len, kv_heads, head_dim, page, rotate_mb=0)
+    total = prompts * prompt_len
+    q = torch.randn(total, heads * head_dim, device="cuda").to(torch.bfloat16)
+    out = torch.empty_like(q)
+    q_start = torch.arange(0, total + 1, prompt_len, dtype=torch.int32, device="cuda")
+    kv_len = torch.full((prompts,), prompt_len, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    sinks = torch.randn(heads, device="cuda") if sink else None
+    blocks = prompts * -(-prompt_len // 128)
+
+    def run(i):
+        ops.prefill_attention_tc(q, out, pool, 0, q_start, kv_len, table, 0, prompts, blocks, heads, kv_heads,
+                                 head_dim, page, window, head_dim ** -0.5, status=status, softcap=softcap, sink=sinks)
+
+    seconds = _time(run, iters, graph=True)
+    if window and window < prompt_len:
+        pairs = window * (window + 1) / 2.0 + (prompt_len - window) * float(window)
+    else:
+        pairs = prompt_len * (prompt_len + 1) / 2.0
+    flops = 4.0 * prompts * heads * head_dim * pairs
+    return {"us": seconds * 1e6, "tflops": flops / seconds / 1e12, "status": int(status.item())}
+
+
+def time_wkv(items, tokens_each, heads, head_dim, width, dtype=torch.bfloat16, iters=10):
+    """The recurrence kernel alone on ``items`` entries of ``tokens_each`` tokens; GB/s over what it must move:
+    five float32 streams in, one row out, and every entry's state matrix in and out."""
+    from types import SimpleNamespace
+
+    from pagedserve_b200.kernels.ops import Ops
+
+    ops = Ops(dtype)
+    total, inner = items * tokens_each, heads * head_dim
+    matrix = heads * head_dim * head_dim
+    streams = torch.randn(5, total, inner, device="cuda")
+    streams[3] = -1.0 + streams[3]                      # the decay's argument: decays spread over (0, 1)
+    x = torch.randn(total, width, device="cuda").to(dtype)
+    state = torch.zeros(items, matrix + width, device="cuda")
+    u, gain = torch.randn(inner, device="cuda"), torch.ones(inner, device="cuda")
+    out = torch.empty(total, inner, dtype=dtype, device="cuda")
+    ctx = SimpleNamespace(q_start=torch.arange(0, total + 1, tokens_each, dtype=torch.int32, device="cuda"),
+                          item_slot=torch.arange(items, dtype=torch.int32, device="cuda"), num_items=items)
+
+    def run(i):
+        ops.wkv_recurrence(streams[0], streams[1], streams[2], streams[3], streams[4], u, gain, 1e-5, x, state,
+                           matrix, ctx, out, heads, head_dim)
+
+    seconds = _time(run, iters, graph=True)
+    nbytes = total * inner * (5 * 4 + out.element_size()) + items * matrix * 4 * 2
+    return {"us": seconds * 1e6, "gbs": nbytes / seconds / 1e9, "tokens_per_s": total / seconds}
+
+
+def time_cache_write(tokens, heads, kv_heads, head_dim, page=16, rot_dims=None, iters=20):
+    """The kernel that turns queries and keys and fills the pages, beside the plain cache write (``kv_append``)
+    of as many tokens; GB/s over queries and keys read and queries, keys and values written."""
+    from types import SimpleNamespace
+
+    from pagedserve_b200.kernels.ops import Ops
+
+    ops = Ops(torch.bfloat16)
+    pool, table, _, stride = _paged_inputs(1, tokens, kv_heads, head_dim, page, rotate_mb=0)
+    q = torch.randn(tokens, heads * head_dim, device="cuda").to(torch.bfloat16)
+    k = torch.randn(tokens, kv_heads * head_dim, device="cuda").to(torch.bfloat16)
+    rot = head_dim if rot_dims is None else rot_dims
+    inv_freq = (10000.0 ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / max(rot, 1))).float().cuda()
+    item = torch.zeros(tokens, dtype=torch.int32, device="cuda")
+    positions = torch.arange(tokens, dtype=torch.int32, device="cuda")
+    layer = SimpleNamespace(k_pool=pool[:, 0, 0], v_pool=pool[:, 0, 1], page_stride=stride, page_size=page,
+                            block_table=table)
+    ctx = SimpleNamespace(token_slot=item, positions=positions)
+    turned = _time(lambda i: ops.rotary_cache_write(q, k, None, inv_freq, rot, True, ctx, layer, heads, kv_heads,
+                                                    head_dim), iters, graph=True)
+    plain = _time(lambda i: ops.kv_append(k, k, item, positions, table, layer.k_pool, layer.v_pool, stride, kv_heads,
+                                          head_dim, page), iters, graph=True)
+    moved = tokens * head_dim * 2 * (2 * heads + 3 * kv_heads)
+    return {"us": turned * 1e6, "gbs": moved / turned / 1e9, "plain_write_us": plain * 1e6,
+            "plain_write_gbs": tokens * head_dim * 2 * 4 * kv_heads / plain / 1e9}
+
+
 def main(argv=None):
     parser = argparse.ArgumentParser(prog="python -m pagedserve_b200.kernels.microbench")
     sub = parser.add_subparsers(dest="kind", required=True)
@@ -144,9 +268,20 @@ def main(argv=None):
     a.add_argument("--page-size", type=int, default=16)
     a.add_argument("--iters", type=int, default=50)
     a.add_argument("--graph", action="store_true", help="replay the calls as one CUDA graph")
+    w = sub.add_parser("wkv")
+    w.add_argument("--items", type=int, default=2)
+    w.add_argument("--tokens", type=int, default=1024, help="tokens of every entry")
+    w.add_argument("--heads", type=int, default=16)
+    w.add_argument("--head-dim", type=int, default=64)
+    w.add_argument("--width", type=int, default=1024)
+    w.add_argument("--iters", type=int, default=10)
     args = parser.parse_args(argv)
     if args.kind == "gemm":
         bench_gemm(args)
+    elif args.kind == "wkv":
+        run = time_wkv(args.items, args.tokens, args.heads, args.head_dim, args.width, iters=args.iters)
+        print(f"wkv recurrence items={args.items} tokens={args.tokens} heads={args.heads} hd={args.head_dim}: "
+              f"{run['us']:.2f} us, {run['gbs']:.0f} GB/s, {run['tokens_per_s'] / 1e6:.2f} M tokens/s")
     else:
         bench_attention(args)
     return 0
