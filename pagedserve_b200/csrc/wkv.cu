@@ -47,6 +47,12 @@ token_shift_mix_kernel(const T* __restrict__ x, int x_stride, const float* __res
     }
 }
 
+// the sum over each half of a warp (lanes 0..15, lanes 16..31), in a fixed order
+__device__ __forceinline__ float half_warp_sum(float v) {
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
 __device__ __forceinline__ void wkv_copy16(float* dst, const float* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
                  : "memory");
@@ -65,7 +71,7 @@ struct WkvLayout {
     static constexpr int PARTS = DMAX / IQ;                             // threads that share a column: 8 or 16
     static constexpr int RUN = IQ == 4 ? 4 : IQ + 4;                    // a part's run of a row, padded against bank conflicts
     static constexpr int ROW = PARTS * RUN;
-    static constexpr int CH = 16;                                       // tokens per chunk
+    static constexpr int CH = DMAX > 64 ? 8 : 16;                       // tokens per chunk
     static constexpr int THREADS = (DMAX / COLS) * PARTS, WARPS = THREADS / 32;
     static constexpr int BUF = 3 * CH * ROW + 2 * CH * DMAX;
     static constexpr int Y = 2 * BUF, BONUS = Y + CH * DMAX, U = BONUS + CH, GAIN = U + DMAX, FLOATS = GAIN + DMAX;
@@ -180,67 +186,109 @@ wkv_recurrence_kernel(const float* __restrict__ r, const float* __restrict__ k, 
             const int padded = tt * ROW + (i / IQ) * RUN + (i % IQ);
             s_w[padded] = expf(-expf(s_w[padded]));
         }
-        for (int tt = warp; tt < n; tt += WARPS) {
+        // (sixteen lanes per token, so that a warp works on two tokens at a time)
+        for (int first = 2 * warp; first < n; first += 2 * WARPS) {
+            const int tt = first + (lane >> 4);
             float p = 0.f;
-            for (int i = lane; i < d; i += 32) {
-                const int padded = tt * ROW + (i / IQ) * RUN + (i % IQ);
-                p = fmaf(s_r[padded] * s_u[i], s_k[padded], p);
-            }
-            p = warp_sum(p);
-            if (lane == 0) s_bonus[tt] = p;
-        }
-        __syncthreads();
-        // the token's operands are read one token ahead of their use
-        float4 rr[Q4], kk[Q4], ww[Q4], vv;
-        auto load = [&](int tt) {
-#pragma unroll
-            for (int q = 0; q < Q4; ++q) {
-                rr[q] = *reinterpret_cast<const float4*>(s_r + tt * ROW + part * RUN + 4 * q);
-                kk[q] = *reinterpret_cast<const float4*>(s_k + tt * ROW + part * RUN + 4 * q);
-                ww[q] = *reinterpret_cast<const float4*>(s_w + tt * ROW + part * RUN + 4 * q);
-            }
-            vv = *reinterpret_cast<const float4*>(s_v + tt * DMAX + j0);
-        };
-        load(0);
-        for (int tt = 0; tt < n; ++tt) {
-            float ri[IQ], ki[IQ], wi[IQ];
-#pragma unroll
-            for (int q = 0; q < Q4; ++q) {
-                ri[4 * q] = rr[q].x; ri[4 * q + 1] = rr[q].y; ri[4 * q + 2] = rr[q].z; ri[4 * q + 3] = rr[q].w;
-                ki[4 * q] = kk[q].x; ki[4 * q + 1] = kk[q].y; ki[4 * q + 2] = kk[q].z; ki[4 * q + 3] = kk[q].w;
-                wi[4 * q] = ww[q].x; wi[4 * q + 1] = ww[q].y; wi[4 * q + 2] = ww[q].z; wi[4 * q + 3] = ww[q].w;
-            }
-            const float vc[4] = {vv.x, vv.y, vv.z, vv.w};
-            if (tt + 1 < n) load(tt + 1);
-            float y[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int ii = 0; ii < IQ; ++ii) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    y[c] = fmaf(ri[ii], s[ii][c], y[c]);
-                    s[ii][c] = fmaf(wi[ii], s[ii][c], ki[ii] * vc[c]);
+            if (tt < n) {
+                for (int i = lane & 15; i < d; i += 16) {
+                    const int padded = tt * ROW + (i / IQ) * RUN + (i % IQ);
+                    p = fmaf(s_r[padded] * s_u[i], s_k[padded], p);
                 }
             }
-            // sum over the parts in a fixed order; on the way every thread keeps fewer columns: 4 -> 2 -> 1
-            const bool odd = part & 1, upper = (part >> 1) & 1;
-            const float got0 = __shfl_xor_sync(0xffffffffu, odd ? y[0] : y[2], 1);
-            const float got1 = __shfl_xor_sync(0xffffffffu, odd ? y[1] : y[3], 1);
-            const float a0 = (odd ? y[2] : y[0]) + got0, a1 = (odd ? y[3] : y[1]) + got1;
-            float b = (upper ? a1 : a0) + __shfl_xor_sync(0xffffffffu, upper ? a0 : a1, 2);
-            b += __shfl_xor_sync(0xffffffffu, b, 4);
-            if (PARTS == 16) b += __shfl_xor_sync(0xffffffffu, b, 8);
-            const float v_mine = mine == 0 ? vc[0] : mine == 1 ? vc[1] : mine == 2 ? vc[2] : vc[3];
-            if (part < 4) s_y[tt * DMAX + j0 + mine] = fmaf(v_mine, s_bonus[tt], b);
+            p = half_warp_sum(p);
+            if ((lane & 15) == 0 && tt < n) s_bonus[tt] = p;
         }
         __syncthreads();
-        // the head norm, the gain and the gate for the chunk's tokens: a warp per token
-        for (int tt = warp; tt < n; tt += WARPS) {
+        // The chunk's tokens in order. Nothing but registers is written here, so that the reads of the tokens
+        // ahead can be scheduled early; each token leaves this thread's share of its four outputs in y[tt].
+        float y[CH][4];
+        auto token = [&](int tt) {
+            const float4 vv = *reinterpret_cast<const float4*>(s_v + tt * DMAX + j0);
+            const float vc[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+            for (int q = 0; q < Q4; ++q) {
+                const float4 rr = *reinterpret_cast<const float4*>(s_r + tt * ROW + part * RUN + 4 * q);
+                const float4 kk = *reinterpret_cast<const float4*>(s_k + tt * ROW + part * RUN + 4 * q);
+                const float4 ww = *reinterpret_cast<const float4*>(s_w + tt * ROW + part * RUN + 4 * q);
+                const float ri[4] = {rr.x, rr.y, rr.z, rr.w}, ki[4] = {kk.x, kk.y, kk.z, kk.w},
+                            wi[4] = {ww.x, ww.y, ww.z, ww.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        y[tt][c] = fmaf(ri[e], s[4 * q + e][c], y[tt][c]);
+                        s[4 * q + e][c] = fmaf(wi[e], s[4 * q + e][c], ki[e] * vc[c]);
+                    }
+                }
+            }
+        };
+#pragma unroll
+        for (int tt = 0; tt < CH; ++tt) y[tt][0] = y[tt][1] = y[tt][2] = y[tt][3] = 0.f;
+        if (n == CH) {
+            // a full chunk is straight-line code: reads of later tokens move ahead of the arithmetic of earlier ones
+#pragma unroll
+            for (int tt = 0; tt < CH; ++tt) token(tt);
+        } else {
+#pragma unroll
+            for (int tt = 0; tt < CH; ++tt)
+                if (tt < n) token(tt);
+        }
+        // The sums over the parts, in a fixed order, for all tokens of the chunk at once: at every step a thread
+        // passes half of what it holds to a neighbour and adds up the other half. Bits 0 and 1 of the part choose
+        // the column, bits 2 and 3 the tokens that stay with a thread.
+        const bool bit0 = part & 1, bit1 = (part >> 1) & 1, bit2 = (part >> 2) & 1, bit3 = (part >> 3) & 1;
+        float a[CH][2];
+#pragma unroll
+        for (int tt = 0; tt < CH; ++tt) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const float keep = bit0 ? y[tt][2 + c] : y[tt][c], send = bit0 ? y[tt][c] : y[tt][2 + c];
+                a[tt][c] = keep + __shfl_xor_sync(0xffffffffu, send, 1);
+            }
+        }
+        float b[CH];
+#pragma unroll
+        for (int tt = 0; tt < CH; ++tt) {
+            const float keep = bit1 ? a[tt][1] : a[tt][0], send = bit1 ? a[tt][0] : a[tt][1];
+            b[tt] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+        }
+        float c2[CH / 2];
+#pragma unroll
+        for (int q = 0; q < CH / 2; ++q) {
+            const float keep = bit2 ? b[q + CH / 2] : b[q], send = bit2 ? b[q] : b[q + CH / 2];
+            c2[q] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+        }
+        const int col = j0 + mine;
+        if constexpr (PARTS == 16) {
+#pragma unroll
+            for (int q = 0; q < CH / 4; ++q) {
+                const float keep = bit3 ? c2[q + CH / 4] : c2[q], send = bit3 ? c2[q] : c2[q + CH / 4];
+                const float total = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+                const int tt = bit2 * (CH / 2) + bit3 * (CH / 4) + q;
+                if (tt < n) s_y[tt * DMAX + col] = fmaf(s_v[tt * DMAX + col], s_bonus[tt], total);
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < CH / 2; ++q) {
+                const int tt = bit2 * (CH / 2) + q;
+                if (tt < n) s_y[tt * DMAX + col] = fmaf(s_v[tt * DMAX + col], s_bonus[tt], c2[q]);
+            }
+        }
+        __syncthreads();
+        // the head norm, the gain and the gate for the chunk's tokens: sixteen lanes per token
+        for (int first = 2 * warp; first < n; first += 2 * WARPS) {
+            const int tt = first + (lane >> 4);
+            const bool valid = tt < n;
             float sq = 0.f;
-            for (int i = lane; i < d; i += 32) sq = fmaf(s_y[tt * DMAX + i], s_y[tt * DMAX + i], sq);
-            const float scale = rsqrtf(warp_sum(sq) * inv_d + eps);
-            T* row = out + (size_t)(t0 + tt) * out_stride + h * d;
-            for (int i = lane; i < d; i += 32)
-                row[i] = from_float<T>(s_y[tt * DMAX + i] * scale * s_gain[i] * s_g[tt * DMAX + i]);
+            if (valid)
+                for (int i = lane & 15; i < d; i += 16) sq = fmaf(s_y[tt * DMAX + i], s_y[tt * DMAX + i], sq);
+            const float scale = rsqrtf(half_warp_sum(sq) * inv_d + eps);
+            if (valid) {
+                T* row = out + (size_t)(t0 + tt) * out_stride + h * d;
+                for (int i = lane & 15; i < d; i += 16)
+                    row[i] = from_float<T>(s_y[tt * DMAX + i] * scale * s_gain[i] * s_g[tt * DMAX + i]);
+            }
         }
     }
 #pragma unroll
