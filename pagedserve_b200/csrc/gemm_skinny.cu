@@ -59,18 +59,35 @@ __device__ __forceinline__ void split_position(int p, int page_size, int* index,
     }
 }
 
+// Several products of equal shape in one launch: output columns [g * cols, (g + 1) * cols) of the stacked weight
+// belong to group g, which reads its own rows of A (A + g * a_stride) and writes its own block of the output
+// (out + g * out_stride, columns counted from the group's first). The activation applies from column act_from
+// of the stacked weight on. cols == 0: one product, as always. cols is a multiple of 16, so that a CTA's 16 weight
+// rows belong to one group.
+struct SkinnyGroups {
+    int cols = 0;
+    long long a_stride = 0;
+    long long out_stride = 0;
+    int act_from = 0;
+};
+
 // MT: token tiles of 8. WARPS: warps per CTA. UNROLL: k steps whose loads a warp issues together (a round);
 // WARPS * UNROLL * 32 >= K makes it one round, so that the latency of the weights is paid once.
 template <int MT, int WARPS, int UNROLL, typename TOut>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bfloat16* __restrict__ W, int ldw,
                    const float* __restrict__ bias, TOut* __restrict__ out, int ldo, int M, int N, int K,
-                   int act, int accumulate, KvScatter kv) {
+                   int act, int accumulate, KvScatter kv, SkinnyGroups gr) {
     // cross-warp sums [WARPS][16][8*MT] floats, then the cache address of each row [8*MT] (64-bit)
     extern __shared__ __align__(16) float red[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * 16;
+    const int group = gr.cols ? n0 / gr.cols : 0;
+    const int n_shift = group * gr.cols;                  // the group's first column of the stacked weight
+    A += group * gr.a_stride;
+    out += group * gr.out_stride;
+    if (gr.cols && n0 < gr.act_from) act = PS_ACT_NONE;
     const int r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);
     const __nv_bfloat16* w0 = W + (size_t)r0 * ldw + 8 * t;
     const __nv_bfloat16* w1 = W + (size_t)r1 * ldw + 8 * t;
@@ -110,7 +127,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
         for (int j = 0; j < EPT; ++j) {
             const int e = threadIdx.x + j * WARPS * 32;
             const int n = n0 + (e & 15), m = e >> 4;
-            prev[j] = (accumulate && e < 16 * TOK && m < M && n < N) ? to_float(out[(size_t)m * ldo + n]) : 0.f;
+            prev[j] = (accumulate && e < 16 * TOK && m < M && n < N) ? to_float(out[(size_t)m * ldo + n - n_shift]) : 0.f;
         }
     };
     // the bias of this thread's output column (the same in every epilogue round: the CTA's thread count is a
@@ -178,30 +195,32 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
             continue;
         }
         v += prev[j];
-        out[(size_t)m * ldo + n] = from_float<TOut>(v);
+        out[(size_t)m * ldo + n - n_shift] = from_float<TOut>(v);
     }
 }
 
 template <int MT, int WARPS, int UNROLL, typename TOut>
 int launch_skinny(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo,
-                  int M, int N, int K, int act, int accumulate, const KvScatter& kv, cudaStream_t s) {
+                  int M, int N, int K, int act, int accumulate, const KvScatter& kv, cudaStream_t s,
+                  const SkinnyGroups& gr = SkinnyGroups{}) {
     size_t smem = (size_t)WARPS * 16 * 8 * MT * sizeof(float) + (size_t)8 * MT * sizeof(long long);
     auto kernel = gemm_skinny_kernel<MT, WARPS, UNROLL, TOut>;
     static size_t raised[MAX_DEVICES] = {0};
     if (!ensure_dynamic_smem((const void*)kernel, smem, raised)) return PS_ERR_LAUNCH;
     return launch_pdl(kernel, dim3((N + 15) / 16), dim3(WARPS * 32), smem, s, (const __nv_bfloat16*)A, lda,
-                      (const __nv_bfloat16*)W, ldw, bias, (TOut*)out, ldo, M, N, K, act, accumulate, kv);
+                      (const __nv_bfloat16*)W, ldw, bias, (TOut*)out, ldo, M, N, K, act, accumulate, kv, gr);
 }
 
 template <int MT, typename TOut>
 int pick_warps(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo, int M,
-               int N, int K, int act, int accumulate, const KvScatter& kv, cudaStream_t s) {
+               int N, int K, int act, int accumulate, const KvScatter& kv, cudaStream_t s,
+               const SkinnyGroups& gr = SkinnyGroups{}) {
     // warps and steps per round such that the k steps of a warp are one round of loads where that is possible
     // (K up to 4,096, at most 8 rows); more token tiles keep the rounds short, their accumulators need the
     // registers
     const int steps = (K + 31) / 32;
 #define PS_SKINNY(W_, U_) \
-    return launch_skinny<MT, W_, U_, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s)
+    return launch_skinny<MT, W_, U_, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s, gr)
     if constexpr (MT >= 2) {
         if (steps <= 32) PS_SKINNY(4, 6);
         if (steps <= 64) PS_SKINNY(8, 6);
@@ -230,11 +249,12 @@ int pick_warps(const void* A, int lda, const void* W, int ldw, const float* bias
 
 template <typename TOut>
 int pick_tiles(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo, int M,
-               int N, int K, int act, int accumulate, const KvScatter& kv, cudaStream_t s) {
+               int N, int K, int act, int accumulate, const KvScatter& kv, cudaStream_t s,
+               const SkinnyGroups& gr = SkinnyGroups{}) {
     // the MMAs of a CTA grow with the token tiles, and from 17 rows on they are what the kernel waits for:
     // every count of tiles has its own instance
 #define PS_TILES(MT_) \
-    return pick_warps<MT_, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s)
+    return pick_warps<MT_, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s, gr)
     switch ((M + 7) / 8) {
         case 1: PS_TILES(1);
         case 2: PS_TILES(2);
@@ -557,6 +577,32 @@ PS_EXPORT int ps_gemm_skinny(const void* A, int lda, const void* W, int ldw, con
         return ps::pick_tiles<float>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
     if (out_dtype == PS_BF16)
         return ps::pick_tiles<__nv_bfloat16>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, kv, s);
+    return PS_ERR_UNSUPPORTED;
+}
+
+// `groups` products of equal shape in one launch: A [groups][M, K] (blocks a_stride elements apart), W the stacked
+// weights [groups * cols, K], out [groups][M, cols] (blocks out_stride elements apart, rows ldo apart); bias
+// (optional) is indexed by the stacked column; the activation applies to the groups from act_from_group on.
+PS_EXPORT int ps_gemm_skinny_grouped(const void* A, int lda, long long a_stride, const void* W, int ldw,
+                                     const float* bias, void* out, int ldo, long long out_stride, int M, int cols,
+                                     int groups, int K, int out_dtype, int act, int act_from_group, void* stream) {
+    if (M <= 0 || cols <= 0 || groups <= 0) return PS_OK;
+    if (M > 64 || cols % 16 != 0) return PS_ERR_UNSUPPORTED;
+    if (K <= 0 || K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || a_stride % 8 != 0 || lda < K || ldw < K || ldo < cols)
+        return PS_ERR_UNSUPPORTED;
+    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return PS_ERR_UNSUPPORTED;
+    ps::KvScatter kv{};
+    ps::SkinnyGroups gr;
+    gr.cols = cols;
+    gr.a_stride = a_stride;
+    gr.out_stride = out_stride;
+    gr.act_from = act_from_group * cols;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int N = groups * cols;
+    if (out_dtype == PS_F32)
+        return ps::pick_tiles<float>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, 0, kv, s, gr);
+    if (out_dtype == PS_BF16)
+        return ps::pick_tiles<__nv_bfloat16>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, 0, kv, s, gr);
     return PS_ERR_UNSUPPORTED;
 }
 

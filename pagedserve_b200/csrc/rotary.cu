@@ -53,7 +53,8 @@ rotary_cache_write_kernel(T* __restrict__ q, int q_stride, const T* __restrict__
     T* q_row = q + (size_t)t * q_stride;
     const T* k_row = k + (size_t)t * k_stride;
     const int total = (n_heads + n_kv_heads) * units;
-    for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+    // few tokens (decode): the heads of a token are shared out over gridDim.y CTAs, one unit per thread
+    for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < total; idx += gridDim.y * blockDim.x) {
         const int head = idx / units, unit = idx - head * units;
         const bool is_query = head < n_heads;
         const int g = head - n_heads;                      // key/value head when not a query
@@ -111,13 +112,15 @@ PS_EXPORT int ps_rotary_cache_write(void* q, int q_stride, const void* k, int k_
     cudaStream_t s = (cudaStream_t)stream;
     const int work = (n_heads + n_kv_heads) * (rot_dims / 2 + head_dim - rot_dims);
     const int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
+    // a step of few tokens is bound by the chain of loads of one thread: spread a token over several CTAs
+    const int split = T >= 512 ? 1 : (work + threads - 1) / threads;
     if (dtype == PS_F32)
-        return ps::launch_pdl(ps::rotary_cache_write_kernel<float>, dim3(T), dim3(threads), 0, s, (float*)q, q_stride,
+        return ps::launch_pdl(ps::rotary_cache_write_kernel<float>, dim3(T, split), dim3(threads), 0, s, (float*)q, q_stride,
                               (const float*)k, k_stride, (const float*)v, v_stride, inv_freq, rot_dims, interleaved,
                               token_row, positions, block_table, bt_stride, (float*)k_pool, (float*)v_pool,
                               page_stride, n_heads, n_kv_heads, head_dim, page_size);
     if (dtype == PS_BF16)
-        return ps::launch_pdl(ps::rotary_cache_write_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, s,
+        return ps::launch_pdl(ps::rotary_cache_write_kernel<__nv_bfloat16>, dim3(T, split), dim3(threads), 0, s,
                               (__nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride,
                               (const __nv_bfloat16*)v, v_stride, inv_freq, rot_dims, interleaved, token_row, positions,
                               block_table, bt_stride, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, page_stride,

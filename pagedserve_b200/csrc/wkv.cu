@@ -38,7 +38,7 @@ token_shift_mix_kernel(const T* __restrict__ x, int x_stride, const float* __res
     const float* before = state + (long long)item_slot[item] * state_stride + prev_offset;
     const T* row = x + (size_t)t * x_stride;
     const T* row_before = x + (size_t)(t > 0 ? t - 1 : 0) * x_stride;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < W; c += gridDim.y * blockDim.x) {
         const float now = to_float(row[c]);
         const float prev = first ? before[c] : to_float(row_before[c]);
         const float delta = prev - now;
@@ -348,12 +348,14 @@ PS_EXPORT int ps_token_shift_mix(const void* x, int x_stride, const float* mu, i
         return PS_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = W >= 256 ? 256 : 128;
+    // few tokens (decode): a row is shared out over several CTAs, one column per thread
+    const int split = T >= 512 ? 1 : (W + threads - 1) / threads;
     if (dtype == PS_F32)
-        return ps::launch_pdl(ps::token_shift_mix_kernel<float>, dim3(T), dim3(threads), 0, s, (const float*)x, x_stride,
+        return ps::launch_pdl(ps::token_shift_mix_kernel<float>, dim3(T, split), dim3(threads), 0, s, (const float*)x, x_stride,
                               mu, n_mix, state, state_stride, prev_offset, token_item, q_start, item_slot, (float*)out,
                               mix_stride, out_stride, W);
     if (dtype == PS_BF16)
-        return ps::launch_pdl(ps::token_shift_mix_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, s,
+        return ps::launch_pdl(ps::token_shift_mix_kernel<__nv_bfloat16>, dim3(T, split), dim3(threads), 0, s,
                               (const __nv_bfloat16*)x, x_stride, mu, n_mix, state, state_stride, prev_offset,
                               token_item, q_start, item_slot, (__nv_bfloat16*)out, mix_stride, out_stride, W);
     return PS_ERR_UNSUPPORTED;

@@ -96,6 +96,7 @@ _SIGNATURES = {
                            _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "ps_gemm_skinny_fused": [_P, _I, _P, _P, _P, _F, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I,
                                  _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "ps_gemm_skinny_grouped": [_P, _I, _L, _P, _I, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _I, _P],
         "ps_paged_attention_decode_checked": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
                                               _F, _I, _I, _P, _P, _P, _P, _P],
         "ps_paged_attention_decode_ex": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I,
@@ -320,6 +321,33 @@ class Ops:
                                         _ptr(out), out.stride(0), M, N, K,
                                         dtype_code(out.dtype), _ACT_CODE[act],
                                         1 if accumulate else 0, *self._kv_arguments(kv, N), _stream()), "gemm_skinny")
+        return out
+
+    GROUPED_ROWS = 32             # most rows for which equal products run as one grouped launch
+
+    def linear_grouped(self, a, w, out, act=None, act_from_group=0):
+        """``out[g] = a[g] @ w[g * cols:(g + 1) * cols].T`` for every group g: ``a`` [G, M, K], ``w`` the stacked
+        weights [G * cols, K], ``out`` [G, M, cols]; ``act`` is applied to the groups from ``act_from_group`` on.
+        Few rows in bfloat16 run as one launch of the weight-streaming kernel; everything else as G products."""
+        groups, M, K = a.shape
+        cols = out.shape[2]
+        if w.shape != (groups * cols, K) or out.shape[:2] != (groups, M):
+            raise KernelError("linear_grouped: shapes do not match")
+        one_launch = (self.dtype == torch.bfloat16 and a.dtype == torch.bfloat16 and M <= self.GROUPED_ROWS
+                      and cols % 16 == 0 and K % 8 == 0 and a.stride(2) == 1 and out.stride(2) == 1
+                      and w.stride(1) == 1 and a.stride(1) % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+                      and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+        if not one_launch:
+            for g in range(groups):
+                self.linear(a[g], w[g * cols:(g + 1) * cols], None, out[g], act=act if g >= act_from_group else None)
+            return out
+        _require(w, "w", torch.bfloat16)
+        _require(out, "out")
+        self.launches += 1
+        _check(self.fast.ps_gemm_skinny_grouped(_ptr(a), a.stride(1), a.stride(0), _ptr(w), w.stride(0), None,
+                                                _ptr(out), out.stride(1), out.stride(0), M, cols, groups, K,
+                                                dtype_code(out.dtype), _ACT_CODE[act], act_from_group, _stream()),
+               "gemm_skinny_grouped")
         return out
 
     def linear_tc(self, a, w, bias, out, act=None, accumulate=False, status=None, bn=0):

@@ -70,7 +70,7 @@ class WkvMixer(Mixer):
     def bind(self, tensors):
         t = lambda name: tensors[self._n(name)]
         self.mu = torch.stack([t("mu." + s) for s in MIXES]).contiguous()          # float32 [5, W]
-        self.w_r, self.w_k, self.w_v, self.w_g = t("r"), t("k"), t("v"), t("g")
+        self.w_rkvg = torch.cat([t("r"), t("k"), t("v"), t("g")], dim=0).contiguous()      # [4 * inner, W]
         self.w1, self.w2, self.w0 = t("w1"), t("w2"), t("w0")
         if self.w1.shape[0] != self.w2.shape[1]:
             raise ValueError("wkv: the two matrices of the decay do not fit each other")
@@ -87,10 +87,8 @@ class WkvMixer(Mixer):
         ops.token_shift_mix(x, self.mu, state, self.state_matrix, ctx, blends)
         # r, k, v, gate, decay argument: float32 rows of one buffer
         streams = ops.empty((5, tokens, self.inner), torch.float32, device)
-        ops.linear(blends[0], self.w_r, None, streams[0])
-        ops.linear(blends[1], self.w_k, None, streams[1])
-        ops.linear(blends[2], self.w_v, None, streams[2])
-        ops.linear(blends[3], self.w_g, None, streams[3], act="silu")
+        # four products of equal shape, each on its own blend; the last one is the gate
+        ops.linear_grouped(blends[:4], self.w_rkvg, streams[:4], act="silu", act_from_group=3)
         low = ops.empty((tokens, self.w1.shape[0]), dtype, device)
         ops.linear(blends[4], self.w1, None, low, act="tanh")
         ops.linear(low, self.w2, self.w0, streams[4])

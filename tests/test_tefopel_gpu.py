@@ -496,3 +496,26 @@ def test_product_epilogues(act, dtype, M, N, K):
     z = a.double() @ w.double().T
     want = {"relu_squared": torch.relu(z) ** 2, "silu": torch.nn.functional.silu(z), "tanh": torch.tanh(z)}[act]
     assert rel_err(out, want) < (1e-5 if dtype == torch.float32 else 5e-3)
+
+
+@pytest.mark.parametrize("dtype,M,groups,cols,K", [(torch.bfloat16, 1, 4, 32, 64), (torch.bfloat16, 8, 4, 96, 200),
+                                                   (torch.bfloat16, 32, 3, 1024, 1024), (torch.bfloat16, 40, 4, 64, 128),
+                                                   (torch.bfloat16, 5, 2, 24, 64), (torch.float32, 6, 4, 32, 48)])
+def test_grouped_products(dtype, M, groups, cols, K):
+    """Several products of equal shape, each on rows of its own, as one call: the one-launch form for few bfloat16
+    rows and the product-by-product form elsewhere give what separate products give; the activation touches only
+    the groups it is asked for."""
+    ops = ops_for(dtype)
+    g = torch.Generator().manual_seed(M + cols)
+    a = torch.randn(groups, M, K, generator=g).to(dtype)
+    w = (torch.randn(groups * cols, K, generator=g) / K ** 0.5).to(dtype)
+    out = torch.full((groups + 1, M, cols), float("nan"), dtype=torch.float32, device=DEV)
+    before = ops.launches
+    ops.linear_grouped(a.to(DEV), w.to(DEV), out[:groups], act="silu", act_from_group=groups - 1)
+    one_launch = dtype == torch.bfloat16 and M <= ops.GROUPED_ROWS and cols % 16 == 0
+    assert ops.launches - before == (1 if one_launch else groups)
+    for index in range(groups):
+        z = a[index].double() @ w[index * cols:(index + 1) * cols].double().T
+        want = torch.nn.functional.silu(z) if index == groups - 1 else z
+        assert rel_err(out[index], want) < (1e-5 if dtype == torch.float32 else 5e-3)
+    assert torch.isnan(out[groups]).all()
