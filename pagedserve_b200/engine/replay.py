@@ -52,7 +52,8 @@ def run(args, stdin=None, stdout=None) -> int:
     os.makedirs(args.out, exist_ok=True)
     pages = -(-args.max_tokens // args.block_size)
     config = EngineConfig(dtype=args.dtype, block_size=args.block_size, num_blocks=pages,
-                          max_num_seqs=args.max_num_seqs, max_num_batched_tokens=4096,
+                          max_num_seqs=args.max_num_seqs,
+                          max_num_batched_tokens=max(4096, pages * args.block_size),   # a step may bring them all
                           max_model_len=pages * args.block_size,       # no request outgrows the pool
                           enable_cuda_graphs=not args.disable_cuda_graphs)
     engine = Engine.from_folder(args.model, config)

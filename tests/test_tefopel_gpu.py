@@ -36,7 +36,12 @@ CONFIG_B = plain.make_config([A(2, 1, 64, window=70, rot_dims=64, ff=96, softcap
 CONFIG_C = plain.make_config([W(1, 40), A(1, 1, 24, window=1, rot_dims=24, ff=52, scale=0.25, softcap=5.0),
                               A(3, 3, 24, window=7, rot_dims=4, ff=None, scale=0.2, softcap=22.0), W(2, 12, ff=36)],
                              width=72, vocab=53, eps=1e-4)
-CONFIGS = {"a": (CONFIG_A, 1, 8, 16), "b": (CONFIG_B, 2, 4, 16), "c": (CONFIG_C, 3, 6, 8)}    # config, seed, rank, page
+# one kind of layer only: a model without any pages, and one without any slot state
+CONFIG_D = plain.make_config([W(2, 32, ff=48), W(1, 20), W(2, 32, ff=48) | {"weights_of": 0}], width=48, vocab=61)
+CONFIG_E = plain.make_config([A(3, 1, 16, window=9, rot_dims=6, ff=40, scale=0.3, softcap=9.0),
+                              A(2, 2, 48, window=33, rot_dims=48, ff=None, base=300.0, softcap=25.0)], width=40, vocab=77)
+CONFIGS = {"a": (CONFIG_A, 1, 8, 16), "b": (CONFIG_B, 2, 4, 16), "c": (CONFIG_C, 3, 6, 8),     # config, seed, rank, page
+           "d": (CONFIG_D, 4, 3, 16), "e": (CONFIG_E, 5, 8, 32)}
 
 _FOLDERS, _TENSORS, _LOGITS = {}, {}, {}
 
@@ -140,6 +145,37 @@ def test_mixed_batches_reuse_pages_and_slots(which, dtype):
     steps = helpers.trace_mixed(sequences, seed=3, live=4, decode_tail=20, max_portion=40)
     assert helpers.peak_tokens(steps) < sum(len(t) for t in sequences.values())
     check_replay(which, dtype, steps, sequences, "mixed")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", ["d", "e"])
+def test_models_of_one_kind_of_layer(which, dtype):
+    sequences = sequences_for(which, [70, 3, 131, 29, 64, 1], seed=70)
+    check_replay(which, dtype, helpers.trace_whole(sequences), sequences, "whole")
+    steps = helpers.trace_mixed(sequences, seed=5, live=4, decode_tail=16, max_portion=30)
+    check_replay(which, dtype, steps, sequences, "mixed")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_prompt_longer_than_the_usual_step(dtype):
+    """2,100 tokens in one step (more than the engine's default token budget of a step), and the same prompt in
+    portions with a decoded tail: keys thousands of positions back, angles of thousands of radians, a recurrent
+    state that has seen thousands of tokens."""
+    sequences = sequences_for("a", [2100], seed=80)
+    wanted = list(range(0, 2100, 97)) + list(range(2040, 2100))
+    whole = [{"step": 0, "entries": [{"id": "s0", "tokens": sequences["s0"], "want": wanted}], "end": ["s0"]}]
+    got = run_replay("a", dtype, whole)
+    want = plain_logits("a", sequences)["s0"][wanted]
+    helpers.assert_close(got["s0"], want, dtype, "long prompt in one step")
+    steps, number, done = [], 0, 0
+    for size in [1000, 700, 340] + [1] * 60:
+        places = [i for i in range(size) if done + i in wanted]
+        steps.append({"step": number, "entries": [{"id": "s0", "tokens": sequences["s0"][done:done + size],
+                                                   "want": places}], "end": []})
+        number, done = number + 1, done + size
+    steps[-1]["end"] = ["s0"]
+    got = run_replay("a", dtype, steps)
+    helpers.assert_close(got["s0"], want, dtype, "long prompt in portions")
 
 
 def test_long_decoding_float32():
