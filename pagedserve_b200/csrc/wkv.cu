@@ -322,6 +322,138 @@ int launch_wkv(const float* r, const float* k, const float* v, const float* deca
                       (T*)out, out_stride, heads, d);
 }
 
+// eight consecutive elements as floats (16-byte loads; the address is 16-byte aligned)
+__device__ __forceinline__ void load8(const float* p, float (&o)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&o)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* pair = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(pair[i]);
+        o[2 * i] = f.x;
+        o[2 * i + 1] = f.y;
+    }
+}
+
+// wkv_prepare: everything between the residual stream and the mixer's large products, for one token per CTA:
+//   x[t]   = rms_norm(h[t]) * gain, rounded to the compute type (as the norm kernel rounds it)
+//   m_s[t] = x[t] + (x[t-1] - x[t]) * mu_s for s = 0 .. 3, written as blends; x[t] itself is written too
+//   m_w    = the fifth blend, kept in shared memory
+//   low    = tanh(W1 m_w)                      (rank numbers, rounded to the compute type)
+//   decay[t] = W2 low + w0                     (float32; the argument of exp(-exp(.)))
+// x[t-1] of an entry's first token is the slot's `last`; other tokens norm the row before their own themselves.
+template <typename T>
+__global__ void __launch_bounds__(256)
+wkv_prepare_kernel(const float* __restrict__ h, int ld_h, const float* __restrict__ gain, float eps,
+                   const float* __restrict__ mu, const float* __restrict__ state, long long state_stride,
+                   int prev_offset, const int* __restrict__ token_item, const int* __restrict__ q_start,
+                   const int* __restrict__ item_slot, const T* __restrict__ w1, int ld_w1, int rank,
+                   const T* __restrict__ w2, int ld_w2, const float* __restrict__ w0, int inner,
+                   T* __restrict__ blends, long long mix_stride, int ld_blend, float* __restrict__ decay,
+                   int ld_decay, int W) {
+    extern __shared__ __align__(16) float prep_smem[];
+    float* const m_w = prep_smem;                       // [W]
+    float* const low = prep_smem + W;                   // [rank]
+    __shared__ float red[2][8];
+    pdl_prologue();
+    h = pdl_fresh(h);
+    state = pdl_fresh(state);
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int item = token_item[t];
+    const bool first = (t == q_start[item]);
+    const float* before = state + (long long)item_slot[item] * state_stride + prev_offset;
+    const float* row = h + (size_t)t * ld_h;
+    const float* row_before = h + (size_t)(t > 0 ? t - 1 : 0) * ld_h;
+    float ss = 0.f, ss_before = 0.f;
+    for (int c = tid; c < W; c += 256) {
+        const float a = row[c];
+        ss = fmaf(a, a, ss);
+        if (!first) {
+            const float b = row_before[c];
+            ss_before = fmaf(b, b, ss_before);
+        }
+    }
+    ss = warp_sum(ss);
+    ss_before = warp_sum(ss_before);
+    if (lane == 0) { red[0][warp] = ss; red[1][warp] = ss_before; }
+    __syncthreads();
+    float total = 0.f, total_before = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) { total += red[0][w]; total_before += red[1][w]; }
+    const float scale = rsqrtf(total / (float)W + eps), scale_before = rsqrtf(total_before / (float)W + eps);
+    // every CTA of a token (gridDim.y of them when the step has few tokens) makes the whole fifth blend, but
+    // writes only its share of the other blends and of the decay's argument
+    for (int c = tid; c < W; c += 256) {
+        const T now_t = from_float<T>(row[c] * scale * gain[c]);
+        const float now = to_float(now_t);
+        const float prev = first ? before[c] : to_float(from_float<T>(row_before[c] * scale_before * gain[c]));
+        const float delta = prev - now;
+        if ((c >> 8) % gridDim.y == blockIdx.y) {
+#pragma unroll
+            for (int s = 0; s < 4; ++s)
+                blends[(long long)s * mix_stride + (size_t)t * ld_blend + c] = from_float<T>(fmaf(delta, mu[(size_t)s * W + c], now));
+            blends[4 * mix_stride + (size_t)t * ld_blend + c] = now_t;
+        }
+        m_w[c] = to_float(from_float<T>(fmaf(delta, mu[(size_t)4 * W + c], now)));
+    }
+    __syncthreads();
+    const bool wide1 = (W & 7) == 0 && (ld_w1 & 7) == 0 && (((uintptr_t)w1) & 15) == 0;
+    for (int rho = warp; rho < rank; rho += 8) {
+        const T* wr = w1 + (size_t)rho * ld_w1;
+        float acc = 0.f;
+        if (wide1) {
+            for (int c = lane * 8; c < W; c += 256) {
+                float w8[8];
+                load8(wr + c, w8);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc = fmaf(w8[i], m_w[c + i], acc);
+            }
+        } else {
+            for (int c = lane; c < W; c += 32) acc = fmaf(to_float(wr[c]), m_w[c], acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) low[rho] = to_float(from_float<T>(tanhf(acc)));
+    }
+    __syncthreads();
+    const bool wide2 = (rank & 7) == 0 && (ld_w2 & 7) == 0 && (((uintptr_t)w2) & 15) == 0;
+    for (int c = blockIdx.y * 256 + tid; c < inner; c += gridDim.y * 256) {
+        const T* wr = w2 + (size_t)c * ld_w2;
+        float acc = 0.f;
+        if (wide2) {
+            for (int rho = 0; rho < rank; rho += 8) {
+                float w8[8];
+                load8(wr + rho, w8);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc = fmaf(w8[i], low[rho + i], acc);
+            }
+        } else {
+            for (int rho = 0; rho < rank; ++rho) acc = fmaf(to_float(wr[rho]), low[rho], acc);
+        }
+        decay[(size_t)t * ld_decay + c] = acc + w0[c];
+    }
+}
+
+template <typename T>
+int launch_wkv_prepare(const float* h, int ld_h, const float* gain, float eps, const float* mu, const float* state,
+                       long long state_stride, int prev_offset, const int* token_item, const int* q_start,
+                       const int* item_slot, const void* w1, int ld_w1, int rank, const void* w2, int ld_w2,
+                       const float* w0, int inner, void* blends, long long mix_stride, int ld_blend, float* decay,
+                       int ld_decay, int n_tokens, int W, cudaStream_t s) {
+    auto kernel = wkv_prepare_kernel<T>;
+    const size_t smem = (size_t)(W + rank) * sizeof(float);
+    static size_t raised[MAX_DEVICES] = {0};
+    if (!ensure_dynamic_smem((const void*)kernel, smem, raised)) return PS_ERR_LAUNCH;
+    // a step of few tokens is bound by the chain of one CTA's phases: share a token's writes out over several
+    const int widest = W > inner ? W : inner;
+    const int split = n_tokens >= 512 ? 1 : (widest + 255) / 256;
+    return launch_pdl(kernel, dim3(n_tokens, split), dim3(256), smem, s, h, ld_h, gain, eps, mu, state, state_stride,
+                      prev_offset, token_item, q_start, item_slot, (const T*)w1, ld_w1, rank, (const T*)w2, ld_w2, w0,
+                      inner, (T*)blends, mix_stride, ld_blend, decay, ld_decay, W);
+}
+
 template <typename T>
 int pick_wkv(const float* r, const float* k, const float* v, const float* decay, const float* gate, int ld,
              const float* u, const float* gain, float eps, const void* x, int x_stride, int W, float* state,
@@ -380,5 +512,31 @@ PS_EXPORT int ps_wkv_recurrence(const float* r, const float* k, const float* v, 
     if (dtype == PS_BF16)
         return ps::pick_wkv<__nv_bfloat16>(r, k, v, decay, gate, ld, u, gain, eps, x, x_stride, W, state, state_stride,
                                            prev_offset, q_start, item_slot, out, out_stride, n_items, heads, d, s);
+    return PS_ERR_UNSUPPORTED;
+}
+
+// The norm of the residual rows, the five blends (four written to `blends` [5][T, W] together with the normed
+// rows themselves in block 4; the fifth used in place), and the decay's argument W2 tanh(W1 m_w) + w0 (float32).
+// h: float32 [T, W]; gain: the RMS norm's gain; w1 [rank, W], w2 [inner, rank] in the compute type.
+PS_EXPORT int ps_wkv_prepare(const float* h, int ld_h, const float* gain, float eps, const float* mu,
+                             const float* state, long long state_stride, int prev_offset, const int* token_item,
+                             const int* q_start, const int* item_slot, const void* w1, int ld_w1, int rank,
+                             const void* w2, int ld_w2, const float* w0, int inner, void* blends,
+                             long long mix_stride, int ld_blend, float* decay, int ld_decay, int T, int W, int dtype,
+                             void* stream) {
+    if (T <= 0) return PS_OK;
+    if (!h || !gain || !mu || !state || !token_item || !q_start || !item_slot || !w1 || !w2 || !w0 || !blends || !decay)
+        return PS_ERR_BAD_ARGUMENT;
+    if (W <= 0 || rank <= 0 || inner <= 0) return PS_ERR_BAD_ARGUMENT;
+    if ((size_t)(W + rank) * sizeof(float) > 200 * 1024) return PS_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == PS_F32)
+        return ps::launch_wkv_prepare<float>(h, ld_h, gain, eps, mu, state, state_stride, prev_offset, token_item,
+                                             q_start, item_slot, w1, ld_w1, rank, w2, ld_w2, w0, inner, blends,
+                                             mix_stride, ld_blend, decay, ld_decay, T, W, s);
+    if (dtype == PS_BF16)
+        return ps::launch_wkv_prepare<__nv_bfloat16>(h, ld_h, gain, eps, mu, state, state_stride, prev_offset,
+                                                     token_item, q_start, item_slot, w1, ld_w1, rank, w2, ld_w2, w0,
+                                                     inner, blends, mix_stride, ld_blend, decay, ld_decay, T, W, s);
     return PS_ERR_UNSUPPORTED;
 }

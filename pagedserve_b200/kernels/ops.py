@@ -80,6 +80,8 @@ _SIGNATURES = {
         "ps_rotary_cache_write": [_P, _I, _P, _I, _P, _I, _P, _I, _I, _P, _P, _P, _I, _P, _P, _L, _I, _I, _I, _I, _I,
                                   _I, _P],
         "ps_token_shift_mix": [_P, _I, _P, _I, _P, _L, _I, _P, _P, _P, _P, _L, _I, _I, _I, _I, _P],
+        "ps_wkv_prepare": [_P, _I, _P, _F, _P, _P, _L, _I, _P, _P, _P, _P, _I, _I, _P, _I, _P, _I, _P, _L, _I, _P, _I, _I,
+                           _I, _I, _P],
         "ps_wkv_recurrence": [_P, _P, _P, _P, _P, _I, _P, _P, _F, _P, _I, _I, _P, _L, _I, _P, _P, _P, _I, _I, _I, _I,
                               _I, _P],
         "ps_sample": [_P, _I, _I, _I, _P, _P, _P, _I, _P, _P],
@@ -774,6 +776,33 @@ class Ops:
                                             _ptr(ctx.item_slot), _ptr(out), out.stride(0), out.stride(1), T, W,
                                             self.code, _stream()), "token_shift_mix")
         return out
+
+    def wkv_prepare(self, hidden, gain, eps, mu, state, prev_offset, ctx, w1, w2, w0, blends, decay):
+        """From the float32 residual rows to the wkv mixer's inputs in one launch: the RMS norm (``gain``, ``eps``),
+        the blends with the token before (``mu`` float32 [5, W]; ``blends`` [5, T, W]: blocks 0..3 the first four
+        blends, block 4 the normed rows), and the decay's argument ``w2 @ tanh(w1 @ blend_4) + w0`` into
+        ``decay`` (float32 [T, inner] rows)."""
+        T, W = hidden.shape
+        _require(hidden, "hidden", torch.float32)
+        _require(gain, "gain", torch.float32)
+        _require(mu, "mu", torch.float32)
+        _require(state, "state", torch.float32)
+        _require(w1, "w1", self.dtype)
+        _require(w2, "w2", self.dtype)
+        _require(w0, "w0", torch.float32)
+        _require(blends, "blends", self.dtype)
+        _require(decay, "decay", torch.float32)
+        rank, inner = w1.shape[0], w2.shape[0]
+        if (blends.shape != (5, T, W) or blends.stride(2) != 1 or mu.shape != (5, W) or not mu.is_contiguous()
+                or w1.shape[1] != W or w2.shape[1] != rank or w1.stride(1) != 1 or w2.stride(1) != 1
+                or decay.shape != (T, inner) or decay.stride(1) != 1 or hidden.stride(1) != 1 or w0.numel() != inner):
+            raise KernelError("wkv_prepare: shapes do not match")
+        self.launches += 1
+        _check(self.core.ps_wkv_prepare(_ptr(hidden), hidden.stride(0), _ptr(gain), float(eps), _ptr(mu), _ptr(state),
+                                        state.stride(0), prev_offset, _ptr(ctx.token_item), _ptr(ctx.q_start),
+                                        _ptr(ctx.item_slot), _ptr(w1), w1.stride(0), rank, _ptr(w2), w2.stride(0),
+                                        _ptr(w0), inner, _ptr(blends), blends.stride(0), blends.stride(1), _ptr(decay),
+                                        decay.stride(0), T, W, self.code, _stream()), "wkv_prepare")
 
     def wkv_recurrence(self, r, k, v, decay, gate, u, gain, eps, x, state, prev_offset, ctx, out, heads, head_dim):
         """The recurrence of every entry of the step, tokens in order, from and into the slots' state (see

@@ -38,6 +38,7 @@ class WkvMixer(Mixer):
     """
 
     graph_safe = True
+    accepts_deferred_norm = True       # an RMS norm in front is computed by the mixer's first kernel
 
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
@@ -84,14 +85,24 @@ class WkvMixer(Mixer):
         tokens = x.shape[0]
         state = layer.state
         blends = ops.empty((len(MIXES), tokens, self.width), dtype, device)
-        ops.token_shift_mix(x, self.mu, state, self.state_matrix, ctx, blends)
         # r, k, v, gate, decay argument: float32 rows of one buffer
         streams = ops.empty((5, tokens, self.inner), torch.float32, device)
+        prologue = x.norm.fused_prologue() if hasattr(x, "materialize") and hasattr(x.norm, "fused_prologue") else None
+        if prologue is not None and not prologue.has_mean and prologue.bias is None and x.rows is None:
+            # the norm, the blends and the decay's small products in one launch; block 4 of `blends` holds the
+            # normed rows, of which the recurrence keeps each entry's newest
+            ops.wkv_prepare(x.x, prologue.weight, prologue.eps, self.mu, state, self.state_matrix, ctx, self.w1,
+                            self.w2, self.w0, blends, streams[4])
+            x = blends[4]
+        else:
+            if hasattr(x, "materialize"):
+                x = x.materialize()
+            ops.token_shift_mix(x, self.mu, state, self.state_matrix, ctx, blends)
+            low = ops.empty((tokens, self.w1.shape[0]), dtype, device)
+            ops.linear(blends[4], self.w1, None, low, act="tanh")
+            ops.linear(low, self.w2, self.w0, streams[4])
         # four products of equal shape, each on its own blend; the last one is the gate
         ops.linear_grouped(blends[:4], self.w_rkvg, streams[:4], act="silu", act_from_group=3)
-        low = ops.empty((tokens, self.w1.shape[0]), dtype, device)
-        ops.linear(blends[4], self.w1, None, low, act="tanh")
-        ops.linear(low, self.w2, self.w0, streams[4])
         mixed = ops.empty((tokens, self.inner), dtype, device)
         ops.wkv_recurrence(streams[0], streams[1], streams[2], streams[4], streams[3], self.u, self.gain,
                            float(p["eps"]), x, state, self.state_matrix, ctx, mixed, p["n_heads"], p["head_dim"])

@@ -555,3 +555,45 @@ def test_grouped_products(dtype, M, groups, cols, K):
         want = torch.nn.functional.silu(z) if index == groups - 1 else z
         assert rel_err(out[index], want) < (1e-5 if dtype == torch.float32 else 5e-3)
     assert torch.isnan(out[groups]).all()
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 5e-6), (torch.bfloat16, 1e-2)])
+@pytest.mark.parametrize("width,inner,rank", [(64, 32, 8), (72, 40, 5), (1024, 512, 16), (200, 192, 3)])
+def test_wkv_first_kernel_norms_blends_and_decays(dtype, tol, width, inner, rank):
+    """The mixer's first kernel alone: RMS norm of the residual rows, blends with the row before (the slot's
+    stored row for an entry's first token), and the decay's argument, against the plain functions."""
+    from types import SimpleNamespace
+
+    ops = ops_for(dtype)
+    g = torch.Generator().manual_seed(width + rank)
+    lengths, slots = [6, 1, 19], [1, 3, 0]
+    T = sum(lengths)
+    hidden = 3.0 * torch.randn(T, width, generator=g)
+    gain = 1.0 + 0.2 * torch.randn(width, generator=g)
+    mu = torch.rand(5, width, generator=g)
+    w1 = (torch.randn(rank, width, generator=g) / width ** 0.5).to(dtype)
+    w2 = torch.randn(inner, rank, generator=g).to(dtype)
+    w0 = torch.randn(inner, generator=g)
+    matrix = 7
+    state = torch.zeros(4, matrix + width)
+    state[0, matrix:] = torch.randn(width, generator=g).to(dtype).float()      # entry 2 continues a request
+    starts = np.concatenate([[0], np.cumsum(lengths)])
+    ctx = SimpleNamespace(token_item=torch.tensor(np.repeat(np.arange(3), lengths), dtype=torch.int32, device=DEV),
+                          q_start=torch.tensor(starts, dtype=torch.int32, device=DEV),
+                          item_slot=torch.tensor(slots, dtype=torch.int32, device=DEV), num_items=3)
+    blends = torch.full((5, T, width), float("nan"), dtype=dtype, device=DEV)
+    decay = torch.full((T, inner), float("nan"), dtype=torch.float32, device=DEV)
+    eps = 1e-5
+    ops.wkv_prepare(hidden.to(DEV), gain.to(DEV), eps, mu.to(DEV), state.to(DEV), matrix, ctx, w1.to(DEV), w2.to(DEV),
+                    w0.to(DEV), blends, decay)
+    normed = plain.rms_unit(hidden.double(), eps) * gain.double()
+    assert rel_err(blends[4], normed) < tol
+    x = blends[4].cpu().double()                           # the kernel's own rounding of the normed rows
+    for item, (length, slot) in enumerate(zip(lengths, slots)):
+        sl = slice(starts[item], starts[item + 1])
+        for s in range(4):
+            want = plain.token_shift(x[sl], mu[s].double(), first=state[slot, matrix:].double())
+            assert rel_err(blends[s, sl], want) < tol
+        m_w = plain.token_shift(x[sl], mu[4].double(), first=state[slot, matrix:].double())
+        want = torch.tanh(m_w @ w1.double().T) @ w2.double().T + w0.double()
+        assert rel_err(decay[sl], want) < 2 * tol
