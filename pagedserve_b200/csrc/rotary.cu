@@ -18,7 +18,19 @@
 
 namespace ps {
 
-constexpr int ROTARY_MAX_PAIRS = 256;                      // turning pairs of a head: head sizes up to 512
+constexpr int ROTARY_MAX_PAIRS = 256;
+
+// two neighbouring elements as one access
+template <typename T> struct PairOf;
+template <> struct PairOf<float> { using type = float2; };
+template <> struct PairOf<__nv_bfloat16> { using type = __nv_bfloat162; };
+__device__ __forceinline__ float2 pair_to_float(float2 v) { return v; }
+__device__ __forceinline__ float2 pair_to_float(__nv_bfloat162 v) { return __bfloat1622float2(v); }
+template <typename P> __device__ __forceinline__ P pair_from_float(float a, float b);
+template <> __device__ __forceinline__ float2 pair_from_float<float2>(float a, float b) { return make_float2(a, b); }
+template <> __device__ __forceinline__ __nv_bfloat162 pair_from_float<__nv_bfloat162>(float a, float b) {
+    return __floats2bfloat162_rn(a, b);
+}                      // turning pairs of a head: head sizes up to 512
 
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -53,6 +65,41 @@ rotary_cache_write_kernel(T* __restrict__ q, int q_stride, const T* __restrict__
     T* q_row = q + (size_t)t * q_stride;
     const T* k_row = k + (size_t)t * k_stride;
     const int total = (n_heads + n_kv_heads) * units;
+    // Neighbouring pairs, an even head size and even strides: every pair of a head, turning or not, is one access
+    // of two elements (the addresses below are then multiples of the pair's size).
+    using P = typename PairOf<T>::type;
+    const bool by_pairs = interleaved && !(head_dim & 1) && !(q_stride & 1) && !(k_stride & 1) && !(v_stride & 1) &&
+                          !(page_stride & 1) &&
+                          !(((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)k_pool | (uintptr_t)v_pool) &
+                            (sizeof(P) - 1));
+    if (by_pairs) {
+        const int pairs = head_dim >> 1;
+        const int total_pairs = (n_heads + n_kv_heads) * pairs;
+        for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < total_pairs; idx += gridDim.y * blockDim.x) {
+            const int head = idx / pairs, u = idx - head * pairs;
+            const bool turns = u < half;
+            const float cs = turns ? turn[u].x : 1.f, sn = turns ? turn[u].y : 0.f;
+            if (head < n_heads) {
+                if (!turns) continue;
+                P* at = reinterpret_cast<P*>(q_row + head * head_dim) + u;
+                const float2 ab = pair_to_float(*at);
+                *at = pair_from_float<P>(ab.x * cs - ab.y * sn, ab.y * cs + ab.x * sn);
+            } else if (page_base >= 0) {
+                const int g = head - n_heads;
+                const P key = reinterpret_cast<const P*>(k_row + g * head_dim)[u];
+                const long long dst = page_base + (long long)g * page_size * head_dim + 2 * u;
+                P turned = key;
+                if (turns) {
+                    const float2 ab = pair_to_float(key);
+                    turned = pair_from_float<P>(ab.x * cs - ab.y * sn, ab.y * cs + ab.x * sn);
+                }
+                *reinterpret_cast<P*>(k_pool + dst) = turned;
+                *reinterpret_cast<P*>(v_pool + dst) =
+                    v ? reinterpret_cast<const P*>(v + (size_t)t * v_stride + g * head_dim)[u] : key;
+            }
+        }
+        return;
+    }
     // few tokens (decode): the heads of a token are shared out over gridDim.y CTAs, one unit per thread
     for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < total; idx += gridDim.y * blockDim.x) {
         const int head = idx / units, unit = idx - head * units;

@@ -422,7 +422,7 @@ def test_attention_window_edge_and_far_key_stand_out(kernel, dtype, head_dim, to
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,head_dim,rot_dims,page", [(4, 2, 16, 8, 16), (3, 3, 24, 24, 8), (2, 1, 64, 0, 4),
-                                                                   (1, 1, 10, 6, 2)])
+                                                                   (1, 1, 10, 6, 2), (2, 1, 9, 4, 4), (3, 1, 7, 6, 8)])
 @pytest.mark.parametrize("own_values", [False, True])
 def test_rotary_kernel_turns_queries_and_fills_pages(dtype, heads, kv_heads, head_dim, rot_dims, page, own_values):
     from test_kernels_gpu import PagedCase
@@ -468,7 +468,8 @@ def test_rotary_kernel_turns_queries_and_fills_pages(dtype, heads, kv_heads, hea
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 6e-6), (torch.bfloat16, 8e-3)])     # float32: sums of up to 128 terms
-@pytest.mark.parametrize("heads,dim,width", [(2, 16, 64), (1, 40, 72), (3, 64, 200), (2, 128, 96), (5, 12, 36)])
+@pytest.mark.parametrize("heads,dim,width", [(2, 16, 64), (1, 40, 72), (3, 64, 200), (2, 128, 96), (5, 12, 36),
+                                             (2, 96, 64), (1, 80, 40), (3, 30, 48)])
 def test_wkv_kernels_alone(dtype, tol, heads, dim, width):
     """Token shift and the recurrence on three entries at once (one of a single token, one that continues stored
     state), against the plain recurrence; the state left in the slots is checked too."""
