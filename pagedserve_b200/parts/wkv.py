@@ -32,6 +32,11 @@ class WkvMixer(Mixer):
     Decay, exponentials, state, the head norm and the gate's product are float32; r, k, v, the gate and the
     decay's argument leave their products as float32 too.
 
+    Launches of a step: given an RMS norm not yet computed, one kernel norms the residual rows, makes the blends
+    and the decay's argument (``wkv_prepare``); given normed rows, the blend kernel and two small products do.
+    Then r, k, v and the gate as one grouped product where rows are few (four products otherwise), the
+    recurrence, and the output projection.
+
     params: hidden_size, n_heads, head_dim, eps, decay_rank (inner size of W_w1 / W_w2; None: whatever the
     file holds), random_decay_rank (the size random weights are drawn with where decay_rank is None);
     the tensors are mu.r ... mu.w, r, k, v, g, w1, w2, w0, u, norm, o.
