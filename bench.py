@@ -302,12 +302,8 @@ def _run_reference(args, ref):
 
 # ---------------------------------------------------------------------------------------------------------
 # --design tefopel: the design's prefill and decode throughput beside GPT-2 of equal size, and its kernels alone
-DESIGN_SIZES = {
-    # name: width, heads, head size, inner size, layers, wkv heads (of size 64), window
-    "w1024": dict(width=1024, heads=16, head_dim=64, ff=4096, layers=8, wkv_heads=16, window=1024),
-    "w2048": dict(width=2048, heads=16, head_dim=128, ff=8192, layers=8, wkv_heads=32, window=1024),
-}
-DESIGN_VOCAB, DESIGN_CONTEXT = 32000, 2048
+DESIGN_SIZES = {"w1024": "tefopel-w1024", "w2048": "tefopel-w2048"}      # named sizes of config/tefopel.py
+DESIGN_CONTEXT = 2048
 
 
 def design_arm(args):
@@ -320,7 +316,6 @@ def design_arm(args):
 
     from pagedserve_b200.config.engine_config import EngineConfig
     from pagedserve_b200.config.gpt2 import GPT2Config
-    from pagedserve_b200.config.tefopel import TefopelConfig, attention_layer, wkv_layer
     from pagedserve_b200.engine.batch import StepEntry
     from pagedserve_b200.engine.engine import Engine
     from pagedserve_b200.kernels import microbench
@@ -329,18 +324,13 @@ def design_arm(args):
     rng = np.random.default_rng(0)
     steps, warmup = min(args.steps, 64), max(args.warmup, 3)
 
-    def configs(size):
-        layers = []
-        for index in range(size["layers"]):
-            if index % 4 == 3:
-                layers.append(wkv_layer(size["wkv_heads"], 64, ff=size["ff"]))
-            else:
-                layers.append(attention_layer(size["heads"], size["heads"], size["head_dim"], size["window"],
-                                              size["ff"], rot_dims=size["head_dim"] // 2))
-        tefopel = TefopelConfig(vocab=DESIGN_VOCAB, width=size["width"], norm_eps=1e-5, layers=layers)
+    def configs(name):
+        from pagedserve_b200.config import tefopel as sizes
+
+        size = sizes.NAMED_CONFIGS[name]
         gpt2 = GPT2Config(n_layer=size["layers"], n_embd=size["width"], n_head=size["heads"], n_inner=size["ff"],
-                          vocab_size=DESIGN_VOCAB, n_positions=DESIGN_CONTEXT)
-        return {"tefopel": tefopel, "gpt2": gpt2}
+                          vocab_size=size["vocab"], n_positions=DESIGN_CONTEXT)
+        return size, {"tefopel": sizes.named_config(name), "gpt2": gpt2}
 
     def timed(fn):
         torch.cuda.synchronize()
@@ -395,8 +385,8 @@ def design_arm(args):
     report = {"impl": "ours", "design": args.design, "dtype": args.dtype, "data": "synthetic (random weights, uniform ids)",
               "steps": steps, "warmup": warmup, "peaks": peaks, "models": {}, "kernels": {}}
     for name in (args.design_sizes.split(",") if args.design_sizes else DESIGN_SIZES):
-        size = DESIGN_SIZES[name]
-        report["models"][name] = {"size": size, **{kind: measure(config) for kind, config in configs(size).items()}}
+        size, pair = configs(DESIGN_SIZES[name])
+        report["models"][name] = {"size": size, **{kind: measure(config) for kind, config in pair.items()}}
         both = report["models"][name]
         both["tefopel_over_gpt2"] = {key: both["tefopel"][key] / both["gpt2"][key]
                                      for key in ("prefill_tok_s", "decode_b8_tok_s", "decode_b64_tok_s")}

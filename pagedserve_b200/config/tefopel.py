@@ -151,3 +151,30 @@ def wkv_layer(heads: int, dim: int, ff: Optional[int] = None, weights_of: Option
     if weights_of is not None:
         layer["weights_of"] = weights_of
     return layer
+
+
+def repeating_config(width: int, heads: int, head_dim: int, ff: int, layers: int, wkv_heads: int, window: int,
+                     vocab: int, wkv_dim: int = 64, every: int = 4, eps: float = 1e-5) -> TefopelConfig:
+    """A model for random weights: attention layers with every ``every``-th layer a wkv layer, a feed-forward in
+    each, rotation on half of every head."""
+    entries = []
+    for index in range(layers):
+        if index % every == every - 1:
+            entries.append(wkv_layer(wkv_heads, wkv_dim, ff=ff))
+        else:
+            entries.append(attention_layer(heads, heads, head_dim, window, ff, rot_dims=(head_dim // 4) * 2))
+    return TefopelConfig(vocab=vocab, width=width, norm_eps=eps, layers=entries)
+
+
+# sizes that the command line and the benchmark know by name (random weights)
+NAMED_CONFIGS = {
+    "tefopel-tiny": dict(width=64, heads=4, head_dim=16, ff=128, layers=4, wkv_heads=2, window=24, vocab=512, wkv_dim=16),
+    "tefopel-w1024": dict(width=1024, heads=16, head_dim=64, ff=4096, layers=8, wkv_heads=16, window=1024, vocab=32000),
+    "tefopel-w2048": dict(width=2048, heads=16, head_dim=128, ff=8192, layers=8, wkv_heads=32, window=1024, vocab=32000),
+}
+
+
+def named_config(name: str) -> TefopelConfig:
+    if name not in NAMED_CONFIGS:
+        raise ConfigError(f"unknown named configuration {name!r}; known: {sorted(NAMED_CONFIGS)}")
+    return repeating_config(**NAMED_CONFIGS[name])

@@ -44,7 +44,12 @@ def build_engine(model: str, seed: int = 0, **engine_options):
         return Engine.from_folder(model, config)
     if model in NAMED_CONFIGS:
         return Engine.random(named_config(model), seed, config)
-    raise ValueError(f"--model must be a model folder or one of {sorted(NAMED_CONFIGS)}; got {model!r}")
+    from pagedserve_b200.config import tefopel
+
+    if model in tefopel.NAMED_CONFIGS:
+        return Engine.random(tefopel.named_config(model), seed, config)
+    known = sorted(NAMED_CONFIGS) + sorted(tefopel.NAMED_CONFIGS)
+    raise ValueError(f"--model must be a model folder or one of {known}; got {model!r}")
 
 
 def build_scheduler(model: str = "tiny-a", scheduling_strategy: str = ORCA_STRATEGY, prefill_chunk_size: int = 16,

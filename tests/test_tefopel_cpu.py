@@ -38,6 +38,17 @@ def test_layer_helpers_write_what_the_reader_reads():
     assert TefopelConfig.from_dict(config.to_dict()).to_dict() == config.to_dict()
 
 
+def test_named_sizes_are_valid_configurations():
+    from pagedserve_b200.config import tefopel
+
+    for name in tefopel.NAMED_CONFIGS:
+        config = tefopel.named_config(name)
+        assert [layer["type"] for layer in config.layers[:4]] == ["attention"] * 3 + ["wkv"]
+        assert TefopelConfig.from_dict(config.to_dict()).to_dict() == config.to_dict()
+    with pytest.raises(ConfigError):
+        tefopel.named_config("tefopel-huge")
+
+
 def broken(change):
     values = copy.deepcopy(CONFIG)
     change(values)

@@ -229,6 +229,10 @@ def test_command_line_runs_a_model_folder(capsys):
     assert main(["--model", folder_of("c"), "--dtype", "bfloat16", "--max-new-tokens", "4", "--block-size", "8",
                  "--num-blocks", "64", "--max-batch-size", "2", "--prompt-ids", "1 2 3 4 5"]) == 0
     assert "request 0:" in capsys.readouterr().out
+    # a named size with random weights
+    assert main(["--model", "tefopel-tiny", "--seed", "3", "--dtype", "float32", "--max-new-tokens", "5",
+                 "--num-blocks", "32", "--max-batch-size", "2", "--prompt-ids", "7 8 9"]) == 0
+    assert "request 0:" in capsys.readouterr().out
 
 
 # ------------------------------------------------------------------ each part alone
