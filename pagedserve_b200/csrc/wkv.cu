@@ -124,9 +124,10 @@ wkv_recurrence_kernel(const float* __restrict__ r, const float* __restrict__ k, 
         float* buf = wkv_smem + (chunk & 1) * L::BUF;
         const int t0 = begin + chunk * CH, n = min(CH, end - t0);
         if (wide) {
-            const int pieces = d >> 2;                                    // 16-byte pieces of a row
-            for (int e = tid; e < n * pieces; e += THREADS) {
-                const int tt = e / pieces, pc = e - tt * pieces, i = pc << 2;
+            // 16-byte pieces: a thread's place in a row is fixed, its token moves by THREADS / (DMAX / 4)
+            constexpr int PIECES = DMAX / 4;
+            const int i = (tid % PIECES) << 2;
+            for (int tt = tid / PIECES; tt < n && i < d; tt += THREADS / PIECES) {
                 const size_t at = (size_t)(t0 + tt) * ld + h * d + i;
                 const int padded = tt * ROW + (i / IQ) * RUN + (i % IQ);
                 wkv_copy16(buf + padded, r + at);
@@ -181,20 +182,38 @@ wkv_recurrence_kernel(const float* __restrict__ r, const float* __restrict__ k, 
         if (chunk + 1 < n_chunks) issue(chunk + 1);           // nobody reads the other buffer any more
         // decay arguments become decays, in place; one number per token for the bonus:
         // y_j gets v_j * sum_i r_i u_i k_i, the part of the sum that the token's own k v^T contributes
-        for (int e = tid; e < n * d; e += THREADS) {
-            const int tt = e / d, i = e - tt * d;
-            const int padded = tt * ROW + (i / IQ) * RUN + (i % IQ);
-            s_w[padded] = expf(-expf(s_w[padded]));
+        {
+            // a thread's channel is fixed (compile-time place in the padded row), its token moves by THREADS / DMAX
+            constexpr int ROUNDS = (CH * DMAX + THREADS - 1) / THREADS;
+            const int i = tid % DMAX, padded_i = (i / IQ) * RUN + (i % IQ);
+            float arg[ROUNDS];
+#pragma unroll
+            for (int k = 0; k < ROUNDS; ++k) {
+                const int tt = tid / DMAX + k * (THREADS / DMAX);
+                arg[k] = (tt < n && i < d) ? s_w[tt * ROW + padded_i] : 0.f;
+            }
+#pragma unroll
+            for (int k = 0; k < ROUNDS; ++k) arg[k] = expf(-expf(arg[k]));
+#pragma unroll
+            for (int k = 0; k < ROUNDS; ++k) {
+                const int tt = tid / DMAX + k * (THREADS / DMAX);
+                if (tt < n && i < d) s_w[tt * ROW + padded_i] = arg[k];
+            }
         }
         // (sixteen lanes per token, so that a warp works on two tokens at a time)
         for (int first = 2 * warp; first < n; first += 2 * WARPS) {
             const int tt = first + (lane >> 4);
             float p = 0.f;
             if (tt < n) {
-                for (int i = lane & 15; i < d; i += 16) {
+                float rk[DMAX / 16];
+#pragma unroll
+                for (int k = 0; k < DMAX / 16; ++k) {
+                    const int i = (lane & 15) + 16 * k;
                     const int padded = tt * ROW + (i / IQ) * RUN + (i % IQ);
-                    p = fmaf(s_r[padded] * s_u[i], s_k[padded], p);
+                    rk[k] = i < d ? s_r[padded] * s_u[i] * s_k[padded] : 0.f;
                 }
+#pragma unroll
+                for (int k = 0; k < DMAX / 16; ++k) p += rk[k];
             }
             p = half_warp_sum(p);
             if ((lane & 15) == 0 && tt < n) s_bonus[tt] = p;
@@ -280,14 +299,24 @@ wkv_recurrence_kernel(const float* __restrict__ r, const float* __restrict__ k, 
         for (int first = 2 * warp; first < n; first += 2 * WARPS) {
             const int tt = first + (lane >> 4);
             const bool valid = tt < n;
-            float sq = 0.f;
-            if (valid)
-                for (int i = lane & 15; i < d; i += 16) sq = fmaf(s_y[tt * DMAX + i], s_y[tt * DMAX + i], sq);
+            float mine_y[DMAX / 16], factor[DMAX / 16], sq = 0.f;
+#pragma unroll
+            for (int k = 0; k < DMAX / 16; ++k) {
+                const int i = (lane & 15) + 16 * k;
+                const bool in = valid && i < d;
+                mine_y[k] = in ? s_y[tt * DMAX + i] : 0.f;
+                factor[k] = in ? s_gain[i] * s_g[tt * DMAX + i] : 0.f;
+            }
+#pragma unroll
+            for (int k = 0; k < DMAX / 16; ++k) sq = fmaf(mine_y[k], mine_y[k], sq);
             const float scale = rsqrtf(half_warp_sum(sq) * inv_d + eps);
             if (valid) {
                 T* row = out + (size_t)(t0 + tt) * out_stride + h * d;
-                for (int i = lane & 15; i < d; i += 16)
-                    row[i] = from_float<T>(s_y[tt * DMAX + i] * scale * s_gain[i] * s_g[tt * DMAX + i]);
+#pragma unroll
+                for (int k = 0; k < DMAX / 16; ++k) {
+                    const int i = (lane & 15) + 16 * k;
+                    if (i < d) row[i] = from_float<T>(mine_y[k] * scale * factor[k]);
+                }
             }
         }
     }
