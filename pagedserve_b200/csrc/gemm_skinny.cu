@@ -83,11 +83,14 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, int lda, const __nv_bflo
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int n0 = blockIdx.x * 16;
-    const int group = gr.cols ? n0 / gr.cols : 0;
-    const int n_shift = group * gr.cols;                  // the group's first column of the stacked weight
-    A += group * gr.a_stride;
-    out += group * gr.out_stride;
-    if (gr.cols && n0 < gr.act_from) act = PS_ACT_NONE;
+    int n_shift = 0;                                      // the group's first column of the stacked weight
+    if (gr.cols) {
+        const int group = n0 / gr.cols;
+        n_shift = group * gr.cols;
+        A += group * gr.a_stride;
+        out += group * gr.out_stride;
+        if (n0 < gr.act_from) act = PS_ACT_NONE;
+    }
     const int r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);
     const __nv_bfloat16* w0 = W + (size_t)r0 * ldw + 8 * t;
     const __nv_bfloat16* w1 = W + (size_t)r1 * ldw + 8 * t;

@@ -372,7 +372,8 @@ def run_attention_kernel(kernel, ops, case, lengths, window, scale, softcap, sin
 ATTENTION_KERNELS = [("simt", torch.float32, 24, 3e-6), ("simt", torch.bfloat16, 40, 8e-3),
                      ("decode", torch.bfloat16, 64, 8e-3), ("decode-one-split", torch.bfloat16, 32, 8e-3),
                      ("prefill", torch.bfloat16, 48, 8e-3), ("tcgen05", torch.bfloat16, 64, 8e-3),
-                     ("tcgen05-two", torch.bfloat16, 128, 8e-3)]
+                     ("tcgen05-two", torch.bfloat16, 128, 8e-3), ("decode", torch.bfloat16, 256, 8e-3),
+                     ("prefill", torch.bfloat16, 96, 8e-3)]
 
 
 @pytest.mark.parametrize("kernel,dtype,head_dim,tol", ATTENTION_KERNELS)
