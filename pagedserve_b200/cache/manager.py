@@ -13,7 +13,7 @@ What is different here:
   tables, so a group of windowed layers can give back the pages its window has
   passed while a group of full-attention layers keeps all of them.
 * A page id addresses all cache layers of its group at once; the pool of a
-  group is ``[pages, cache layers, 2 (k,v), kv heads, page size, head dim]``.
+  group is ``[pages, cache layers, planes (k,v), kv heads, page size, head dim]``.
 * Every live request also holds a **slot**: an index into fixed-size
   per-request state: on the device its length, last token, sampling
   parameters and block tables (:class:`pagedserve_b200.cache.slots.SlotStore`,
@@ -58,6 +58,8 @@ class KVNeed:
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None      # None: all earlier keys; w: the last w keys
+    planes: int = 2                   # 2: keys and values; 1: one row per token that attention reads as both
+                                      # (a layer that caches a latent from which keys and values are made)
 
 
 @dataclass(frozen=True)
@@ -146,19 +148,22 @@ class CacheGroup:
         # pages behind the allocator's range that belong to no request (padding tokens of a step write there)
         self.scratch_pages = list(range(num_pages, num_pages + scratch_pages))
         if device is not None:
-            shape = (num_pages + scratch_pages, len(self.cache_layers), 2, need.n_kv_heads, page_size,
+            if need.planes not in (1, 2):
+                raise CacheError("a cache layer has one or two planes")
+            shape = (num_pages + scratch_pages, len(self.cache_layers), need.planes, need.n_kv_heads, page_size,
                      need.head_dim)
             self.pool = torch.empty(shape, dtype=dtype, device=device)
 
     # strides in elements, used by the kernels
     @property
     def page_stride(self) -> int:
-        return len(self.cache_layers) * 2 * self.need.n_kv_heads * self.page_size * self.need.head_dim
+        return len(self.cache_layers) * self.need.planes * self.need.n_kv_heads * self.page_size * self.need.head_dim
 
     def layer_views(self, cache_layer: int):
-        """(k, v) views ``[pages, kv heads, page size, head dim]`` of one cache layer."""
+        """(k, v) views ``[pages, kv heads, page size, head dim]`` of one cache layer (the same view twice
+        where the layer has a single plane)."""
         local = self.cache_layers.index(cache_layer)
-        return self.pool[:, local, 0], self.pool[:, local, 1]
+        return self.pool[:, local, 0], self.pool[:, local, self.need.planes - 1]
 
     @property
     def bytes_per_page(self) -> int:

@@ -86,7 +86,7 @@ class Engine:
         for need in kv_needs:
             if need is not None:
                 by_need[need] = by_need.get(need, 0) + 1
-        bytes_per_page = sum(2 * count * need.n_kv_heads * need.head_dim * cfg.block_size * width
+        bytes_per_page = sum(need.planes * count * need.n_kv_heads * need.head_dim * cfg.block_size * width
                              for need, count in by_need.items())
         self.bytes_per_block = bytes_per_page
         if cfg.num_blocks is not None:

@@ -85,6 +85,14 @@ _SIGNATURES = {
         "ps_wkv_recurrence": [_P, _P, _P, _P, _P, _I, _P, _P, _F, _P, _I, _I, _P, _L, _I, _P, _P, _P, _I, _I, _I, _I,
                               _I, _P],
         "ps_sample": [_P, _I, _I, _I, _P, _P, _P, _I, _P, _P],
+        "ps_embed_pair": [_P, _P, _P, _P, _P, _P, _F, _P, _I, _L, _L, _P, _P, _I, _I, _I, _I, _P, _P],
+        "ps_hyper_begin": [_P, _P, _P, _P, _P, _L, _I, _P],
+        "ps_hyper_step": [_P, _P, _P, _P, _P, _P, _L, _I, _P],
+        "ps_latent_prepare": [_P, _I, _P, _I, _P, _F, _P, _I, _P, _P, _P, _I, _P, _L, _I, _P, _I, _I, _I, _I, _I, _I,
+                              _I, _P],
+        "ps_sigmoid_gate": [_P, _I, _P, _I, _I, _I, _I, _P],
+        "ps_moe_route": [_P, _I, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+        "ps_moe_gate_mul": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
         "ps_step_shape": [_I, _P, _P, _P, _I, _I, _I, _I, _P],
         "ps_step_fill": [_I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _L, _P, _I, _I, _I, _I, _P],
         "ps_step_begin": [_P, _P, _P, _P, _P, _P],
@@ -685,7 +693,7 @@ class Ops:
                              n_items, max_blocks, n_heads, n_kv_heads, head_dim, page_size, window, scale,
                              status=None, row_threads=0, item_row=None, softcap=None, sink=None):
         """tcgen05 causal attention of prompt portions (bfloat16, head size 64 or 128).  ``pool`` is the cache
-        group's whole pool ``[pages, layers, 2, kv heads, page size, head dim]``; ``cache_layer_local`` the
+        group's whole pool ``[pages, layers, planes, kv heads, page size, head dim]`` (one plane: the values are the keys); ``cache_layer_local`` the
         layer's index inside it; ``max_blocks`` >= the number of 128-query blocks of the items.
         ``row_threads``: 1 or 2 threads per query row (0: the kernel's launcher decides)."""
         _require(q, "q", torch.bfloat16)
@@ -694,13 +702,14 @@ class Ops:
             self._tc = _declare(_load_library("tc"), "tc")
         if status is None:
             status = self.status_flag(q.device)
-        pages, layers, two, kv_heads, ps, hd = pool.shape
+        pages, layers, planes, kv_heads, ps, hd = pool.shape
         rows_per_tensor = kv_heads * ps                      # rows of one (layer, k or v) inside a page
-        page_rows = layers * 2 * rows_per_tensor
+        page_rows = layers * planes * rows_per_tensor
         self.launches += 1
         _check(self._tc.ps_prefill_attention_tc(
             _ptr(q), q.stride(0), q.shape[0], _ptr(out), out.stride(0), _ptr(pool), pages * page_rows,
-            (cache_layer_local * 2) * rows_per_tensor, (cache_layer_local * 2 + 1) * rows_per_tensor, page_rows,
+            (cache_layer_local * planes) * rows_per_tensor,
+            (cache_layer_local * planes + planes - 1) * rows_per_tensor, page_rows,
             _ptr(q_start), _ptr(kv_len), _ptr(block_table), block_table.stride(0), _ptr(item_row), first_item,
             n_items, max_blocks, n_heads, n_kv_heads, head_dim, page_size, window or 0, scale, row_threads,
             _ptr(status), float(softcap or 0.0), _ptr(sink), _stream()),
@@ -830,6 +839,156 @@ class Ops:
                                            _ptr(out), out.stride(0), ctx.num_items, heads, head_dim, self.code,
                                            _stream()), "wkv_recurrence")
         return out
+
+    # ------------------------------------------------------------------ embedding with a hashed pair table
+    def embed_pair(self, ctx, table, scale, pair, buckets, mul_prev, mul_cur, newest, out):
+        """out[t] = scale * table[id_t] + pair[row_t] as float32 [T, H]; row_t is the hash
+        (id_{t-1} * mul_prev + id_t * mul_cur) mod buckets, or ``buckets`` for a sequence's first token.  The token
+        before an entry's first token is read from ``newest`` (int32, one per slot), which then receives the
+        entry's last token.  ``pair`` None: no pair table."""
+        T, H = out.shape
+        _require(out, "out", torch.float32)
+        _require(table, "table", self.dtype)
+        if table.shape[1] != H or ctx.token_ids.numel() != T:
+            raise KernelError("embed_pair: shapes do not match")
+        if pair is not None:
+            _require(pair, "pair", self.dtype)
+            _require(newest, "newest", torch.int32)
+            if pair.shape != (buckets + 1, H) or not pair.is_contiguous():
+                raise KernelError("embed_pair: the pair table must hold buckets + 1 rows of the model's width")
+        if not table.is_contiguous() or not out.is_contiguous():
+            raise KernelError("embed_pair: tensors must be contiguous")
+        self.launches += 1
+        _check(self.core.ps_embed_pair(_ptr(ctx.token_ids), _ptr(ctx.positions), _ptr(ctx.token_item),
+                                       _ptr(ctx.q_start), _ptr(ctx.item_slot), _ptr(table), float(scale), _ptr(pair),
+                                       int(buckets), int(mul_prev) % max(int(buckets), 1),
+                                       int(mul_cur) % max(int(buckets), 1), _ptr(newest), _ptr(out), T, H,
+                                       table.shape[0], self.code, _ptr(ctx.status), _stream()), "embed_pair")
+        return out
+
+    # ------------------------------------------------------------------ several residual streams
+    def hyper_begin(self, x0, w_in, streams, u, y):
+        """streams[s] = x0 for every s; u = sum_s w_in[s] * x0; y = 0.  All float32; ``streams`` [S, T, W]."""
+        S = streams.shape[0]
+        for name, tensor in (("x0", x0), ("w_in", w_in), ("streams", streams), ("u", u), ("y", y)):
+            _require(tensor, name, torch.float32)
+        if (streams.shape[1:] != x0.shape or u.shape != x0.shape or y.shape != x0.shape or w_in.numel() != S
+                or not (x0.is_contiguous() and streams.is_contiguous() and u.is_contiguous() and y.is_contiguous())):
+            raise KernelError("hyper_begin: shapes do not match")
+        self.launches += 1
+        _check(self.core.ps_hyper_begin(_ptr(x0), _ptr(w_in), _ptr(streams), _ptr(u), _ptr(y), x0.numel(), S,
+                                        _stream()), "hyper_begin")
+
+    def hyper_step(self, streams, y, mix, w_out, w_in_next, u):
+        """Finish a sublayer and open the next: x_t <- sum_s mix[s, t] x_s + w_out[t] y for every stream t, then
+        u = sum_t w_in_next[t] x_t (``w_in_next`` None: ones) and y = 0.  All float32."""
+        S = streams.shape[0]
+        for name, tensor in (("streams", streams), ("y", y), ("mix", mix), ("w_out", w_out), ("u", u)):
+            _require(tensor, name, torch.float32)
+        if w_in_next is not None:
+            _require(w_in_next, "w_in_next", torch.float32)
+        if (streams.shape[1:] != y.shape or u.shape != y.shape or mix.shape != (S, S) or w_out.numel() != S
+                or (w_in_next is not None and w_in_next.numel() != S) or not mix.is_contiguous()
+                or not (streams.is_contiguous() and u.is_contiguous() and y.is_contiguous())):
+            raise KernelError("hyper_step: shapes do not match")
+        self.launches += 1
+        _check(self.core.ps_hyper_step(_ptr(streams), _ptr(y), _ptr(mix), _ptr(w_out), _ptr(w_in_next), _ptr(u),
+                                       y.numel(), S, _stream()), "hyper_step")
+
+    # ------------------------------------------------------------------ latent attention
+    def latent_prepare(self, q, down, gain, eps, inv_freq, rot_dims, ctx, layer, q_out, n_heads, flat, turning,
+                       rank, write_cache=True):
+        """Between the input projection and attention of a latent-attention layer (csrc/latent.cu): the latent
+        (``down[:, :rank]``, unit RMS times ``gain``) and the turned shared key part (``down[:, rank:]``) go into
+        the token's place of the layer's single cache plane; the turning part of every query head (the last
+        ``turning`` of its ``flat + turning`` numbers in ``q``) is turned into the last ``turning`` of the head's
+        ``rank + turning`` numbers in ``q_out``."""
+        T = q.shape[0]
+        for name, tensor in (("q", q), ("down", down), ("q_out", q_out)):
+            _require(tensor, name, self.dtype)
+            if tensor.stride(1) != 1:
+                raise KernelError("latent_prepare: innermost stride must be 1")
+        _require(gain, "gain", torch.float32)
+        if (q.shape[1] != n_heads * (flat + turning) or down.shape[1] != rank + turning
+                or q_out.shape[1] != n_heads * (rank + turning) or gain.numel() != rank):
+            raise KernelError("latent_prepare: widths do not match")
+        if rot_dims:
+            _require(inv_freq, "inv_freq", torch.float32)
+            if inv_freq.numel() != rot_dims // 2:
+                raise KernelError("latent_prepare: one frequency per pair of turning dimensions")
+        pools = write_cache and layer is not None and layer.k_pool is not None
+        if pools:
+            _require(layer.k_pool, "k_pool", self.dtype)
+            if layer.k_pool.shape[-1] != rank + turning or layer.k_pool.shape[-3] != 1:
+                raise KernelError("latent_prepare: the cache plane must hold one row of rank + turning per token")
+        self.launches += 1
+        _check(self.core.ps_latent_prepare(
+            _ptr(q), q.stride(0), _ptr(down), down.stride(0), _ptr(gain), float(eps),
+            _ptr(inv_freq) if rot_dims else None, rot_dims, _ptr(ctx.token_slot) if pools else None,
+            _ptr(ctx.positions), _ptr(layer.block_table) if pools else None,
+            layer.block_table.stride(0) if pools else 0, _ptr(layer.k_pool) if pools else None,
+            layer.page_stride if pools else 0, layer.page_size if pools else 1, _ptr(q_out), q_out.stride(0), T,
+            n_heads, flat, turning, rank, self.code, _stream()), "latent_prepare")
+
+    def sigmoid_gate(self, heads, g):
+        """heads *= sigmoid(g), elementwise in float32; both [rows, width] row views of the compute type."""
+        _require(heads, "heads", self.dtype)
+        _require(g, "g", self.dtype)
+        if heads.shape != g.shape or heads.stride(1) != 1 or g.stride(1) != 1:
+            raise KernelError("sigmoid_gate: shapes do not match")
+        self.launches += 1
+        _check(self.core.ps_sigmoid_gate(_ptr(heads), heads.stride(0), _ptr(g), g.stride(0), heads.shape[0],
+                                         heads.shape[1], self.code, _stream()), "sigmoid_gate")
+        return heads
+
+    # ------------------------------------------------------------------ routed experts
+    def moe_route(self, x, router, shared_gate_w, dense, chosen, chosen_w, shared_gate, top, groups, keep):
+        """The router of a layer of experts (csrc/moe.cu): softmax of ``x @ router.T`` in float32, the ``top``
+        largest among the experts of the ``keep`` best of ``groups`` groups (0 or 1 groups: all experts stand),
+        weights normalised to sum 1.  ``dense`` float32 [T, E] gets the weights (0 where not chosen), ``chosen``
+        int32 / ``chosen_w`` float32 [T, top] the election, ``shared_gate`` float32 [T] = sigmoid(x . shared_gate_w)
+        where ``shared_gate_w`` [W] is given."""
+        T, W = x.shape
+        E = router.shape[0]
+        _require(x, "x", self.dtype)
+        _require(router, "router", self.dtype)
+        _require(dense, "dense", torch.float32)
+        _require(chosen, "chosen", torch.int32)
+        _require(chosen_w, "chosen_w", torch.float32)
+        if shared_gate_w is not None:
+            _require(shared_gate_w, "shared_gate_w", self.dtype)
+            _require(shared_gate, "shared_gate", torch.float32)
+            if shared_gate_w.numel() != W or not shared_gate_w.is_contiguous() or shared_gate.numel() != T:
+                raise KernelError("moe_route: the shared gate does not fit")
+        if (router.shape[1] != W or x.stride(1) != 1 or router.stride(1) != 1 or dense.shape != (T, E)
+                or chosen.shape != (T, top) or chosen_w.shape != (T, top)
+                or not (dense.is_contiguous() and chosen.is_contiguous() and chosen_w.is_contiguous())):
+            raise KernelError("moe_route: shapes do not match")
+        self.launches += 1
+        _check(self.core.ps_moe_route(_ptr(x), x.stride(0), _ptr(router), router.stride(0), _ptr(shared_gate_w),
+                                      _ptr(dense), _ptr(chosen), _ptr(chosen_w), _ptr(shared_gate), T, W, E, top,
+                                      int(groups or 0), int(keep or 0), self.code, _stream()), "moe_route")
+
+    def moe_gate_mul(self, gate_up, dense, shared_gate, inner, n_experts, expert_ff):
+        """inner[t, c] = silu(gate_up[t, c]) * gate_up[t, C + c] * weight, C = inner.shape[1]; the weight of a
+        column is ``dense[t, c // expert_ff]`` for the experts' columns and ``shared_gate[t]`` from column
+        ``n_experts * expert_ff`` on (csrc/moe.cu)."""
+        T, C = inner.shape
+        _require(gate_up, "gate_up", self.dtype)
+        _require(inner, "inner", self.dtype)
+        _require(dense, "dense", torch.float32)
+        if (gate_up.shape != (T, 2 * C) or gate_up.stride(1) != 1 or inner.stride(1) != 1
+                or dense.shape != (T, n_experts) or not dense.is_contiguous()):
+            raise KernelError("moe_gate_mul: shapes do not match")
+        if shared_gate is not None:
+            _require(shared_gate, "shared_gate", torch.float32)
+        elif C > n_experts * expert_ff:
+            raise KernelError("moe_gate_mul: columns of a shared expert need its gate")
+        self.launches += 1
+        _check(self.core.ps_moe_gate_mul(_ptr(gate_up), gate_up.stride(0), _ptr(dense), _ptr(shared_gate), _ptr(inner),
+                                         inner.stride(0), T, C, n_experts, expert_ff, self.code, _stream()),
+               "moe_gate_mul")
+        return inner
 
     # ------------------------------------------------------------------ sampling
     def sample(self, logits, temperature, seed, position, out, pos_offset=0):

@@ -102,13 +102,22 @@ class Model:
         return self._needs("cache_need")
 
     def state_needs(self) -> List[Optional[StateNeed]]:
-        return self._needs("state_need")
+        """Slot state per cache layer; state of the embedding itself takes one more index behind them."""
+        needs = self._needs("state_need")
+        own = self.embedding.state_need()
+        return needs + [own] if own is not None else needs
 
     # ------------------------------------------------------------------ forward
     def forward(self, ctx) -> torch.Tensor:
         """Run the tokens of ``ctx`` from the cache; return float32 logits ``[R, V]``."""
-        hidden = self.embedding.forward(ctx, self.positions)
         cache = ctx.cache
+        if self.embedding.state_need() is not None:
+            hidden = self.embedding.forward(ctx, self.positions, state=cache.state.get(self.spec.num_cache_layers))
+        else:
+            hidden = self.embedding.forward(ctx, self.positions)
+        # the arrangement's carrier (the float32 rows themselves unless the blocks say otherwise)
+        schedule = self.spec.schedule
+        hidden = self.blocks[schedule[0].layer].begin(hidden, ctx)
         # what a layer asks of the step arena is dead when the layer is done (the residual stream came first):
         # every layer starts from the same place in it
         arena = getattr(self.env.ops, "arena", None)
@@ -128,6 +137,7 @@ class Model:
                 layer.block_table = ctx.block_tables[group_index]
             layer.state = cache.state.get(entry.cache_layer)
             self.blocks[entry.layer].forward(hidden, ctx, layer)
+        hidden = self.blocks[schedule[-1].layer].end(hidden, ctx)
         if arena is not None:
             arena.release(mark)
         if ctx.num_logit_rows == 0:

@@ -179,3 +179,104 @@ class RotaryAttention(Mixer):
         ops.attention(q, k, v, context, ctx, layer, p["n_heads"], p["n_kv_heads"], p["head_dim"], p.get("window"),
                       float(p["scale"]), write_cache=False, softcap=p.get("softcap"), sink=self.sink)
         ops.linear(context, self.w_out, None, residual, accumulate=True)
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(Mixer):
+    """Attention whose keys and values of all heads are made from one small vector per token, which is all the
+    cache holds.
+
+    With H heads, per head ``flat_dim`` unturned and ``rot_dim`` turning query/key numbers, values of size
+    ``v_dim``, and a latent of size ``kv_rank``:
+    q = x W_q, head by head [flat | turning];  down = x W_dkv (kv_rank + rot_dim numbers): c = its first kv_rank,
+    divided by their root mean square and multiplied by a gain; k_turn = its last rot_dim, one for all heads.
+    Head h has k_flat = W_uk(h) c and v = W_uv(h) c.  Turning parts turn by position (neighbouring pairs, the
+    first ``rotary.dims`` of the rot_dim numbers);  s = (q_flat . k_flat + q_turn . k_turn) * scale over the keys
+    j with 0 <= i - j < ``window``; softmax; the joined heads are multiplied by sigmoid(x W_g) and W_o adds the
+    result into the residual row.
+
+    Since q_flat . W_uk(h) c = (W_uk(h)^T q_flat) . c and sum_j p_j W_uv(h) c_j = W_uv(h) sum_j p_j c_j, attention
+    runs over the cached rows [c | k_turn] themselves: one key/value head of size kv_rank + rot_dim shared by all
+    query heads, queries [W_uk(h)^T q_flat | q_turn], values the same rows (a cache of one plane), and W_uv(h)
+    applied to the first kv_rank numbers of each head's result.  Prompt portions and single tokens take the same
+    path, so a position's result does not depend on how the prompt was cut.
+
+    Launches: the stacked projection (q | down | gate), ``latent_prepare`` (norm of c, turns, cache write), the
+    per-head products with W_uk^T, attention, the per-head products with W_uv, the gate, the output product.
+    Norm statistics, angles, scores and softmax are float32.
+
+    params: hidden_size, n_heads, flat_dim, rot_dim, v_dim, kv_rank, scale, window, eps,
+    rotary (dims, base), init_std, out_init_std; tensors q, dkv, dkv.norm, uk, uv, g, o.
+    """
+
+    graph_safe = True
+    accepts_deferred_norm = True
+
+    def __init__(self, params, prefix, env):
+        super().__init__(params, prefix, env)
+        p = self.params
+        self.row = p["kv_rank"] + p["rot_dim"]                    # the cached row, and the attention head size
+        if not (0 < self.row <= 256):
+            raise ValueError(f"latent_attention: kv_rank + rot_dim = {self.row} is not supported: at most 256")
+        if p.get("window") is not None and p["window"] <= 0:
+            raise ValueError("window must be positive")
+        rotary = p.get("rotary") or dict(dims=0, base=10000.0)
+        if rotary["dims"] < 0 or rotary["dims"] % 2 or rotary["dims"] > p["rot_dim"]:
+            raise ValueError("latent_attention: rotary dims must be even and at most rot_dim")
+        self.q_width = p["n_heads"] * (p["flat_dim"] + p["rot_dim"])
+        self.v_width = p["n_heads"] * p["v_dim"]
+        from pagedserve_b200.parts.positions import RotaryPositions
+
+        self.rotary = RotaryPositions(dict(dims=rotary["dims"], base=rotary["base"], interleaved=True,
+                                           head_dim=max(p["rot_dim"], 1)), prefix, env)
+
+    def cache_need(self):
+        return KVNeed(1, self.row, self.params.get("window"), planes=1)
+
+    def param_specs(self):
+        p = self.params
+        W, H, R = p["hidden_size"], p["n_heads"], p["kv_rank"]
+        std = p.get("init_std", 0.02)
+        return [(ParamSpec(self._n("q"), (self.q_width, W), "matmul"), ("normal", std)),
+                (ParamSpec(self._n("dkv"), (self.row, W), "matmul"), ("normal", std)),
+                (ParamSpec(self._n("dkv.norm"), (R,), "vector"), ("ones_plus_normal", 0.1)),
+                (ParamSpec(self._n("uk"), (H * p["flat_dim"], R), "matmul"), ("normal", R ** -0.5)),
+                (ParamSpec(self._n("uv"), (self.v_width, R), "matmul"), ("normal", R ** -0.5)),
+                (ParamSpec(self._n("g"), (self.v_width, W), "matmul"), ("normal", std)),
+                (ParamSpec(self._n("o"), (W, self.v_width), "matmul"), ("normal", p.get("out_init_std", std)))]
+
+    def bind(self, tensors):
+        p = self.params
+        t = lambda name: tensors[self._n(name)]
+        H, d, R = p["n_heads"], p["flat_dim"], p["kv_rank"]
+        self.w_in = torch.cat([t("q"), t("dkv"), t("g")], dim=0).contiguous()          # [q | down | gate, W]
+        self.gain = t("dkv.norm").contiguous()
+        # W_uk(h)^T stacked head by head: [H * R, d], so that head h's product maps q_flat(h) to R numbers
+        self.w_uk_t = t("uk").reshape(H, d, R).transpose(1, 2).reshape(H * R, d).contiguous()
+        self.w_uv = t("uv").contiguous()                                                # [H * v_dim, R]
+        self.w_o = t("o")
+
+    def forward(self, x, residual, ctx, layer):
+        p = self.params
+        ops, dtype, device = self.env.ops, self.env.dtype, residual.device
+        H, d, r, R, dv = p["n_heads"], p["flat_dim"], p["rot_dim"], p["kv_rank"], p["v_dim"]
+        tokens = x.shape[0]
+        projected = ops.empty((tokens, self.w_in.shape[0]), dtype, device)
+        ops.linear(x, self.w_in, None, projected)
+        q = projected[:, :self.q_width]
+        down = projected[:, self.q_width:self.q_width + self.row]
+        gate = projected[:, self.q_width + self.row:]
+        queries = ops.empty((tokens, H * self.row), dtype, device)
+        ops.latent_prepare(q, down, self.gain, float(p["eps"]), self.rotary.inv_freq(), self.rotary.params["dims"],
+                           ctx, layer, queries, H, d, r, R, write_cache=p.get("write_cache", True))
+        # per head: [T, d] x W_uk(h) -> the first R numbers of the head's attention query
+        ops.linear_grouped(q.view(tokens, H, d + r)[:, :, :d].permute(1, 0, 2), self.w_uk_t,
+                           queries.view(tokens, H, self.row)[:, :, :R].permute(1, 0, 2))
+        context = ops.empty((tokens, H * self.row), dtype, device)
+        ops.attention(queries, None, None, context, ctx, layer, H, 1, self.row, p.get("window"), float(p["scale"]),
+                      write_cache=False)
+        heads = ops.empty((tokens, self.v_width), dtype, device)
+        ops.linear_grouped(context.view(tokens, H, self.row)[:, :, :R].permute(1, 0, 2), self.w_uv,
+                           heads.view(tokens, H, dv).permute(1, 0, 2))
+        ops.sigmoid_gate(heads, gate)
+        ops.linear(heads, self.w_o, None, residual, accumulate=True)

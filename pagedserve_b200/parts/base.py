@@ -87,6 +87,12 @@ class Part:
 class Embedding(Part):
     category = "embedding"
 
+    def state_need(self) -> Optional[StateNeed]:
+        """Per-request state of the embedding itself (a table indexed by more than the current token); the model
+        gives it a cache layer of its own behind those of the schedule and passes the tensor to ``forward`` as
+        ``state``."""
+        return None
+
     def forward(self, ctx, positions: "PositionEncoding") -> torch.Tensor:
         raise NotImplementedError
 
@@ -165,6 +171,18 @@ class Block(Part):
 
     def forward(self, hidden: torch.Tensor, ctx, layer: LayerContext) -> None:
         raise NotImplementedError
+
+    # What runs through the layers need not be the one float32 row per token that the embedding makes: an
+    # arrangement with a carrier of its own (several residual streams, say) builds it from the embedded rows
+    # before the first layer (``begin``), gets it as ``hidden`` in every ``forward``, and turns it back into one
+    # row per token behind the last layer (``end``).  ``following`` is the block of the next run of the
+    # schedule (None behind the last): what a block leaves undone for the next one to fold into its first pass.
+    # All blocks of a model share one kind of carrier.
+    def begin(self, hidden: torch.Tensor, ctx):
+        return hidden
+
+    def end(self, carrier, ctx) -> torch.Tensor:
+        return carrier
 
 
 class Head(Part):

@@ -2,7 +2,10 @@
 
 from __future__ import annotations
 
+import torch
+
 from pagedserve_b200.parts.base import Block, register_part
+from pagedserve_b200.weights.loader import ParamSpec
 
 
 @register_part("block", "pre_norm")
@@ -34,3 +37,102 @@ class PreNormBlock(Block):
             return
         self.feed_forward.forward(self._normed(self.norms["pre_feed_forward"], self.feed_forward, hidden),
                                   hidden, ctx)
+
+
+class StreamCarrier:
+    """What runs through the layers of a model with several residual streams: the streams ``[S, T, W]``, the
+    row ``u`` that the open sublayer reads, the row ``y`` it adds its result into, and the (mix, out) weights of
+    a sublayer that has run but whose update of the streams is still to be done."""
+
+    def __init__(self, streams, u, y):
+        self.streams = streams
+        self.u = u
+        self.y = y
+        self.pending = None
+
+
+@register_part("block", "hyper_pre_norm")
+class HyperPreNormBlock(Block):
+    """A pre-norm layer over S residual streams x_1 .. x_S instead of one (all equal to the embedded rows at the
+    start, summed at the end).  For each sublayer f (the mixer, then the feed-forward if the layer has one) with
+    its own weights in[S], out[S], mix[S, S]:
+
+        u = sum_s in[s] x_s;   y = f(norm(u));   x_t <- sum_s mix[s, t] x_s + out[t] y   (all t from the old x)
+
+    Everything is float32.  The update of one sublayer and the read of the next are one pass over the streams
+    (``ops.hyper_step``): a sublayer leaves its update pending and whatever comes next (the feed-forward, the
+    next layer, the end of the model) does it together with its own read.  The sublayer adds its result into a
+    zeroed row, exactly as it would into the residual row of a plain layer, so every mixer and feed-forward
+    works here unchanged.
+
+    params: streams, names (a dict: mixer -> prefix of its three tensors, feed_forward -> likewise), init_std;
+    tensors are ``<prefix>.in``, ``<prefix>.out``, ``<prefix>.mix``."""
+
+    graph_safe = True
+
+    def _sublayers(self):
+        names = self.params["names"]
+        if getattr(self.feed_forward, "is_empty", False):
+            return [names["mixer"]]
+        return [names["mixer"], names["feed_forward"]]
+
+    @property
+    def required_norms(self):
+        if getattr(self.feed_forward, "is_empty", False):
+            return ("pre_mixer",)
+        return ("pre_mixer", "pre_feed_forward")
+
+    def param_specs(self):
+        S = self.params["streams"]
+        if not (isinstance(S, int) and 0 < S <= 8):
+            raise ValueError("hyper_pre_norm: between 1 and 8 streams")
+        std = self.params.get("init_std", 0.1)
+        specs = []
+        for name in self._sublayers():
+            specs += [(ParamSpec(self._n(name + ".in"), (S,), "vector"), ("ones_plus_normal", std)),
+                      (ParamSpec(self._n(name + ".out"), (S,), "vector"), ("ones_plus_normal", std)),
+                      (ParamSpec(self._n(name + ".mix"), (S, S), "vector"), ("eye_plus_normal", std))]
+        return specs
+
+    def bind(self, tensors):
+        self.weights = [tuple(tensors[self._n(f"{name}.{which}")].contiguous() for which in ("in", "out", "mix"))
+                        for name in self._sublayers()]
+
+    def begin(self, hidden, ctx):
+        ops, S = self.env.ops, self.params["streams"]
+        streams = ops.empty((S,) + tuple(hidden.shape), torch.float32, hidden.device)
+        u = ops.empty(hidden.shape, torch.float32, hidden.device)
+        y = ops.empty(hidden.shape, torch.float32, hidden.device)
+        ops.hyper_begin(hidden, self.weights[0][0], streams, u, y)
+        return StreamCarrier(streams, u, y)
+
+    def _open(self, carrier, w_in):
+        """Make ``carrier.u`` the input of the sublayer whose read weights are ``w_in`` (None: the plain sum)."""
+        if carrier.pending is None:
+            return                                 # ``begin`` of this very block has done it
+        w_out, mix = carrier.pending
+        self.env.ops.hyper_step(carrier.streams, carrier.y, mix, w_out, w_in, carrier.u)
+        carrier.pending = None
+
+    @staticmethod
+    def _normed(norm, consumer, rows):
+        if getattr(consumer, "accepts_deferred_norm", False) and hasattr(norm, "defer"):
+            return norm.defer(rows)
+        return norm.forward(rows)
+
+    def forward(self, hidden, ctx, layer):
+        carrier = hidden
+        w_in, w_out, mix = self.weights[0]
+        self._open(carrier, w_in)
+        self.mixer.forward(self._normed(self.norms["pre_mixer"], self.mixer, carrier.u), carrier.y, ctx, layer)
+        carrier.pending = (w_out, mix)
+        if len(self.weights) > 1:
+            w_in, w_out, mix = self.weights[1]
+            self._open(carrier, w_in)
+            self.feed_forward.forward(self._normed(self.norms["pre_feed_forward"], self.feed_forward, carrier.u),
+                                      carrier.y, ctx)
+            carrier.pending = (w_out, mix)
+
+    def end(self, carrier, ctx):
+        self._open(carrier, None)
+        return carrier.u

@@ -34,6 +34,56 @@ class TokenEmbedding(Embedding):
         return hidden
 
 
+@register_part("embedding", "token_pair_embedding")
+class TokenPairEmbedding(TokenEmbedding):
+    """hidden[t] = scale * table[id_t] + pair[row_t]: the token table times a constant, plus a row of a second
+    table chosen by a hash of the token and the one before it, row_t = (id_{t-1} * mul_prev + id_t * mul_cur) mod
+    buckets; the first token of a sequence takes the table's extra last row (index ``buckets``).  Without
+    ``pair`` only the scale is left.
+
+    The token before a step's first token of a request is part of the request's state: one int32 in its slot
+    (``state_need``), read and then replaced by the kernel that embeds the entry's first token.  The sum is
+    float32.  params: vocab_size, hidden_size, name, init_std, scale, pair (None or a dict: name, buckets,
+    mul_prev, mul_cur, init_std)."""
+
+    graph_safe = True
+
+    def __init__(self, params, prefix, env):
+        super().__init__(params, prefix, env)
+        pair = self.params.get("pair")
+        if pair is not None and not (isinstance(pair["buckets"], int) and pair["buckets"] > 0):
+            raise ValueError("token_pair_embedding: buckets must be a positive integer")
+
+    def state_need(self):
+        from pagedserve_b200.cache.manager import StateNeed
+
+        return StateNeed((1,), "int32") if self.params.get("pair") else None
+
+    def param_specs(self):
+        specs = super().param_specs()
+        pair = self.params.get("pair")
+        if pair:
+            specs.append((ParamSpec(self._n(pair["name"]), (pair["buckets"] + 1, self.params["hidden_size"]), "table"),
+                          ("normal", pair.get("init_std", 0.02))))
+        return specs
+
+    def bind(self, tensors):
+        super().bind(tensors)
+        pair = self.params.get("pair")
+        self.pair_table = tensors[self._n(pair["name"])].contiguous() if pair else None
+
+    def forward(self, ctx, positions, state=None):
+        p = self.params
+        pair = p.get("pair") or {}
+        hidden = self.env.ops.empty((ctx.num_tokens, p["hidden_size"]), torch.float32, self.table.device)
+        if self.pair_table is not None and state is None:
+            raise ValueError("token_pair_embedding: the cache holds no slot state for the token before")
+        self.env.ops.embed_pair(ctx, self.table, float(p.get("scale", 1.0)), self.pair_table, pair.get("buckets", 0),
+                                pair.get("mul_prev", 0), pair.get("mul_cur", 0), state, hidden)
+        positions.add_to_hidden(hidden, ctx)
+        return hidden
+
+
 @register_part("head", "lm_head")
 class LMHead(Head):
     """logits = x table^T in float32, no bias; ``tied`` uses the token embedding's table
