@@ -126,6 +126,18 @@ __device__ __forceinline__ float gelu_tanh_fast(float x) {       // tanh.approx:
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// Rows grouped by expert: the rows of A are sorted so that every tile of 128 rows belongs to one expert (or to none:
+// -1, such a tile is skipped by every warp), and tile t reads the weight rows of expert tile_expert[t], which lie
+// rows_per_expert rows and k_per_expert columns apart in the stacked weight matrix (matrices stacked by rows: K
+// columns each, rows_per_expert = their rows; matrices side by side along K: rows_per_expert = 0 and
+// k_per_expert = their columns).  tile_expert null: one weight matrix for all rows.
+struct TileExperts {
+    const int* tile_expert;
+    int rows_per_expert;
+    int k_per_expert;
+    int experts;
+};
+
 template <int BN> struct Config {
     static constexpr int STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
     static constexpr int STAGES = BN > 128 ? 4 : (BN >= 96 ? 5 : 6);
@@ -146,7 +158,8 @@ template <int BN, typename TOut, bool TMA_OUT>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const __grid_constant__ CUtensorMap map_out, const float* __restrict__ bias, TOut* __restrict__ out,
-               int ldo, int M, int N, int K, int act, int accumulate, int* __restrict__ status, KvScatter kv) {
+               int ldo, int M, int N, int K, int act, int accumulate, int* __restrict__ status, KvScatter kv,
+               TileExperts ex) {
     using Cfg = Config<BN>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ unsigned char smem_raw[];
@@ -187,24 +200,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ------------------------------------------------ TMA producer
         if (lane == 0) {
             // the weight tiles of the first stages (of this CTA's first tile) go out before the wait
-            const uint32_t early = ((int)blockIdx.x < num_tiles) ? (uint32_t)min(STAGES, num_kb) : 0u;
+            // (not where tiles choose their weights by a table that a kernel of this step has just written)
+            const uint32_t early = ((int)blockIdx.x < num_tiles && !ex.tile_expert) ? (uint32_t)min(STAGES, num_kb) : 0u;
             for (uint32_t kb = 0; kb < early; ++kb) {
                 const int n0 = ((int)blockIdx.x % tiles_n) * BN;
                 mbar_expect_tx(&full[kb], Cfg::STAGE_BYTES);
                 tma_load_2d(tiles + (size_t)kb * Cfg::STAGE_BYTES + BM * BK * 2, &map_w, (int)kb * BK, n0, &full[kb]);
             }
             pdl_prologue();
+            const int* tile_expert = pdl_fresh(ex.tile_expert);
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+                const int m0 = (tile / tiles_n) * BM;
+                int n0 = (tile % tiles_n) * BN, k0 = 0;
+                if (tile_expert) {
+                    const int expert = tile_expert[tile / tiles_n];
+                    if (expert < 0) continue;
+                    n0 += expert * ex.rows_per_expert;          // the weight rows and columns of this tile's expert
+                    k0 = expert * ex.k_per_expert;
+                }
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     unsigned char* a_dst = tiles + (size_t)s * Cfg::STAGE_BYTES;
                     if (it >= early) {
                         if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { ok = false; atomicExch(status, 11); break; }
                         mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
-                        tma_load_2d(a_dst + BM * BK * 2, &map_w, kb * BK, n0, &full[s]);
+                        tma_load_2d(a_dst + BM * BK * 2, &map_w, k0 + kb * BK, n0, &full[s]);
                     }
                     tma_load_2d(a_dst, &map_a, kb * BK, m0, &full[s]);
                 }
@@ -221,7 +243,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                        ((uint32_t)(BM >> 4) << 24);
             uint32_t it = 0, local = 0;
             bool ok = true;
+            const int* tile_expert = pdl_fresh(ex.tile_expert);
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+                if (tile_expert && tile_expert[tile / tiles_n] < 0) { --local; continue; }     // a tile of no expert
                 const int buf = local & 1;
                 if (!mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag)) { ok = false; atomicExch(status, 12); break; }
                 tc_fence_after();
@@ -248,7 +272,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         uint32_t local = 0;
         [[maybe_unused]] uint32_t chunk = 0;                // column groups this team has sent out so far
         bool ok = true;
+        const int* tile_expert = pdl_fresh(ex.tile_expert);
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+            if (tile_expert && tile_expert[tile / tiles_n] < 0) { --local; continue; }         // a tile of no expert
             const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
             const int buf = local & 1;
             // a q|k|v product whose key and value columns go straight into the pages: where this row's go
@@ -518,34 +544,37 @@ static int sm_count() {
 template <int BN, typename TOut, bool TMA_OUT>
 int launch_kernel(const CUtensorMap& map_a, const CUtensorMap& map_w, const CUtensorMap& map_out, const float* bias,
                   void* out, int ldo, int M, int N, int K, int act, int accumulate, int* status, const KvScatter& kv,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, const TileExperts& ex) {
     auto kernel = gemm_tc_kernel<BN, TOut, TMA_OUT>;
     static size_t raised[MAX_DEVICES] = {0};
     if (!ensure_dynamic_smem((const void*)kernel, (size_t)Config<BN>::SMEM, raised)) return PS_ERR_LAUNCH;
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = tiles < sm_count() ? tiles : sm_count();
     return launch_pdl(kernel, dim3(grid), dim3(THREADS), Config<BN>::SMEM, stream, map_a, map_w, map_out, bias,
-                      (TOut*)out, ldo, M, N, K, act, accumulate, status, kv);
+                      (TOut*)out, ldo, M, N, K, act, accumulate, status, kv, ex);
 }
 
 template <int BN, typename TOut>
 int launch(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo, int M, int N, int K,
-           int act, int accumulate, int* status, const KvScatter& kv, cudaStream_t stream) {
+           int act, int accumulate, int* status, const KvScatter& kv, cudaStream_t stream, const TileExperts& ex) {
     CUtensorMap map_a, map_w, map_out;
-    if (!make_map(&map_a, A, M, K, lda, BM) || !make_map(&map_w, W, N, K, ldw, BN)) return PS_ERR_LAUNCH;
+    const int w_rows = ex.tile_expert ? (ex.experts - 1) * ex.rows_per_expert + N : N;
+    const int w_cols = ex.tile_expert ? (ex.experts - 1) * ex.k_per_expert + K : K;
+    if (!make_map(&map_a, A, M, K, lda, BM) || !make_map(&map_w, W, w_rows, w_cols, ldw, BN)) return PS_ERR_LAUNCH;
     // TMA can write the output when its rows start on 16-byte boundaries
     const bool tma_out = (((uintptr_t)out & 15) == 0) && (((size_t)ldo * sizeof(TOut)) % 16 == 0) &&
                          make_out_map(&map_out, out, M, N, ldo, (int)sizeof(TOut));
     if (tma_out)
-        return launch_kernel<BN, TOut, true>(map_a, map_w, map_out, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream);
+        return launch_kernel<BN, TOut, true>(map_a, map_w, map_out, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream, ex);
     if (kv.k_pool) return PS_ERR_UNSUPPORTED;      // the cache write lives in the TMA-store epilogue only
     map_out = map_a;    // unused
-    return launch_kernel<BN, TOut, false>(map_a, map_w, map_out, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream);
+    return launch_kernel<BN, TOut, false>(map_a, map_w, map_out, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream, ex);
 }
 
 template <typename TOut>
 int pick(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo, int M, int N, int K,
-         int act, int accumulate, int* status, int bn, const KvScatter& kv, cudaStream_t stream) {
+         int act, int accumulate, int* status, int bn, const KvScatter& kv, cudaStream_t stream,
+         const TileExperts& ex = TileExperts{nullptr, 0, 0, 0}) {
     if (bn == 0) {
         const int tiles_m = (M + BM - 1) / BM;
         // widest tile that still gives the SMs enough tiles (measured on B200: 128 wide wins until the
@@ -574,13 +603,13 @@ int pick(const void* A, int lda, const void* W, int ldw, const float* bias, void
         else if (2 * t128 >= sm_count()) bn = 128;
         else bn = 64;
     }
-    if (bn == 256) return launch<256, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream);
-    if (bn == 192) return launch<192, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream);
-    if (bn == 128) return launch<128, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream);
+    if (bn == 256) return launch<256, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream, ex);
+    if (bn == 192) return launch<192, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream, ex);
+    if (bn == 128) return launch<128, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream, ex);
     if constexpr (sizeof(TOut) == 4) {      // 96 columns are three 32-column groups of float32; bfloat16 groups are 64 wide
-        if (bn == 96) return launch<96, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream);
+        if (bn == 96) return launch<96, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream, ex);
     }
-    if (bn == 64) return launch<64, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream);
+    if (bn == 64) return launch<64, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream, ex);
     return PS_ERR_BAD_ARGUMENT;
 }
 
@@ -591,7 +620,8 @@ int pick(const void* A, int lda, const void* W, int ldw, const float* bias, void
 // bn: 0 = choose, else 64, 96 (float32 output only), 128, 192 or 256 (the N extent of the MMA tile).
 static int gemm_tc_entry(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo, int M,
                          int N, int K, int out_dtype, int act, int accumulate, int* status, int bn,
-                         const ps::KvScatter& kv, void* stream) {
+                         const ps::KvScatter& kv, void* stream,
+                         const ps::tc::TileExperts& ex = ps::tc::TileExperts{nullptr, 0, 0, 0}) {
     if (M <= 0 || N <= 0) return PS_OK;
     if (!status) return PS_ERR_BAD_ARGUMENT;
     // TMA: 16-byte aligned base, row stride a multiple of 16 bytes
@@ -599,13 +629,14 @@ static int gemm_tc_entry(const void* A, int lda, const void* W, int ldw, const f
         return PS_ERR_UNSUPPORTED;
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return PS_ERR_UNSUPPORTED;
     if (accumulate && out_dtype != PS_F32) return PS_ERR_BAD_ARGUMENT;
+    if (ex.tile_expert && ex.k_per_expert % 8 != 0) return PS_ERR_UNSUPPORTED;      // TMA: x in units of 16 bytes
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == PS_F32) {
         if (kv.k_pool) return PS_ERR_UNSUPPORTED;
-        return ps::tc::pick<float>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, bn, kv, s);
+        return ps::tc::pick<float>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, bn, kv, s, ex);
     }
     if (out_dtype == PS_BF16)
-        return ps::tc::pick<__nv_bfloat16>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, bn, kv, s);
+        return ps::tc::pick<__nv_bfloat16>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, bn, kv, s, ex);
     return PS_ERR_UNSUPPORTED;
 }
 
@@ -613,6 +644,20 @@ PS_EXPORT int ps_gemm_tc(const void* A, int lda, const void* W, int ldw, const f
                          int N, int K, int out_dtype, int act, int accumulate, int* status, int bn, void* stream) {
     ps::KvScatter none = {};
     return gemm_tc_entry(A, lda, W, ldw, bias, out, ldo, M, N, K, out_dtype, act, accumulate, status, bn, none, stream);
+}
+
+// Rows sorted by expert: A [M, K] whose tiles of 128 rows each belong to one expert, W the experts' matrices
+// stacked by rows ([experts * N, K], along_k = 0) or side by side ([N, experts * K], along_k = 1); tile t of A is
+// multiplied by the matrix of expert tile_expert[t], or skipped (its output rows are left as they are) where
+// tile_expert[t] < 0.  tile_expert: device int32 [ceil(M / 128)], which an earlier kernel on the same stream may
+// have written.
+PS_EXPORT int ps_gemm_tc_experts(const void* A, int lda, const void* W, int ldw, void* out, int ldo, int M, int N,
+                                 int K, int out_dtype, int act, const int* tile_expert, int experts, int along_k,
+                                 int* status, void* stream) {
+    if (!tile_expert || experts <= 0) return PS_ERR_BAD_ARGUMENT;
+    ps::KvScatter none = {};
+    ps::tc::TileExperts ex{tile_expert, along_k ? 0 : N, along_k ? K : 0, experts};
+    return gemm_tc_entry(A, lda, W, ldw, nullptr, out, ldo, M, N, K, out_dtype, act, 0, status, 0, none, stream, ex);
 }
 
 // The packed q|k|v projection of a step with prompt portions: columns [0, q_width) go to `out` (bfloat16), the

@@ -25,7 +25,7 @@ constexpr int LATENT_MAX_PAIRS = 256;
 template <typename T>
 __global__ void __launch_bounds__(256)
 latent_prepare_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ down, int down_stride,
-                      const float* __restrict__ gain, float eps, const float* __restrict__ inv_freq, int rot_dims,
+                      const float* __restrict__ gain, float eps, const float2* __restrict__ inv_freq, int rot_dims,
                       const int* __restrict__ token_row, const int* __restrict__ positions,
                       const int* __restrict__ block_table, int bt_stride, T* __restrict__ pool, long long page_stride,
                       int page_size, T* __restrict__ q_out, int q_out_stride, int n_heads, int flat, int turning,
@@ -41,9 +41,15 @@ latent_prepare_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
     const int half = rot_dims >> 1;
     const float pos = (float)p;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        // the angle p * f to more than one float: f comes as (high, low) parts, the product's rounding error is
+        // recovered with an fma, and what does not fit the float that sincosf takes is applied to first order
+        // (at position 1,000 a rounded angle is off by up to 3e-5 radians, which the scores would show)
+        const float2 f = inv_freq[i];
+        const float high = pos * f.x;
+        const float low = fmaf(pos, f.x, -high) + pos * f.y;
         float sn, cs;
-        sincosf(pos * inv_freq[i], &sn, &cs);
-        turn[i] = make_float2(cs, sn);
+        sincosf(high, &sn, &cs);
+        turn[i] = make_float2(fmaf(-low, sn, cs), fmaf(low, cs, sn));
     }
     const T* row = down + (size_t)t * down_stride;
     float sq = 0.f;
@@ -116,7 +122,8 @@ sigmoid_gate_kernel(T* __restrict__ heads, int heads_stride, const T* __restrict
 }  // namespace ps
 
 // q [T, n_heads * (flat + turning)], down [T, rank + turning] (row views of the projection's output);
-// gain float32 [rank]; inv_freq float32 [rot_dims / 2]; pool: the layer's single cache plane
+// gain float32 [rank]; inv_freq float32 [rot_dims / 2][2]: every frequency as a float and the float nearest to
+// what the first one misses; pool: the layer's single cache plane
 // [pages, 1, page_size, rank + turning] with page_stride elements between pages (null: no cache write);
 // q_out [T, n_heads * (rank + turning)]: only the last `turning` numbers of every head are written.
 PS_EXPORT int ps_latent_prepare(const void* q, int q_stride, const void* down, int down_stride, const float* gain,
@@ -129,18 +136,18 @@ PS_EXPORT int ps_latent_prepare(const void* q, int q_stride, const void* down, i
         return PS_ERR_BAD_ARGUMENT;
     if (!q || !down || !gain || !positions || !q_out || (rot_dims > 0 && !inv_freq)) return PS_ERR_BAD_ARGUMENT;
     if (pool && (!token_row || !block_table || page_size <= 0)) return PS_ERR_BAD_ARGUMENT;
-    if (rot_dims / 2 > ps::LATENT_MAX_PAIRS) return PS_ERR_UNSUPPORTED;
+    if (rot_dims / 2 > ps::LATENT_MAX_PAIRS || ((uintptr_t)inv_freq & 7)) return PS_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = rank + n_heads * turning >= 256 ? 256 : 128;
     if (dtype == PS_F32)
         return ps::launch_pdl(ps::latent_prepare_kernel<float>, dim3(T), dim3(threads), 0, s, (const float*)q, q_stride,
-                              (const float*)down, down_stride, gain, eps, inv_freq, rot_dims, token_row, positions,
-                              block_table, bt_stride, (float*)pool, page_stride, page_size, (float*)q_out,
+                              (const float*)down, down_stride, gain, eps, (const float2*)inv_freq, rot_dims, token_row,
+                              positions, block_table, bt_stride, (float*)pool, page_stride, page_size, (float*)q_out,
                               q_out_stride, n_heads, flat, turning, rank);
     if (dtype == PS_BF16)
         return ps::launch_pdl(ps::latent_prepare_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, s,
                               (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)down, down_stride, gain, eps,
-                              inv_freq, rot_dims, token_row, positions, block_table, bt_stride, (__nv_bfloat16*)pool,
+                              (const float2*)inv_freq, rot_dims, token_row, positions, block_table, bt_stride, (__nv_bfloat16*)pool,
                               page_stride, page_size, (__nv_bfloat16*)q_out, q_out_stride, n_heads, flat, turning,
                               rank);
     return PS_ERR_UNSUPPORTED;

@@ -11,10 +11,13 @@
 // Results: dense weights [T, E] (0 where an expert is not chosen), the chosen experts and their weights
 // [T, top], and the shared gate [T].
 //
-// moe_gate_mul: inner[t, c] = silu(gate[t, c]) * up[t, c] * weight[t, expert of column c], where gate and up are
-// the two halves of one stacked product over all experts' columns, columns [e * F, (e + 1) * F) belong to expert
-// e and the columns from E * F on to the shared expert (weight = the shared gate).  Products in float32, rounded
-// once.
+// moe_gate_mul: inner[t, c] = silu(gate) * up * weight[t, expert of column c] over one stacked product of all
+// experts: expert e's block of 2 F columns is its gate columns, then its up columns; the shared expert's block
+// follows the experts' (weight = the shared gate).  inner's columns [e * F, (e + 1) * F) belong to expert e, those
+// from E * F on to the shared expert.  Products in float32, rounded once.
+//
+// With many tokens the rows are sorted by expert instead (moe_plan, moe_gather, the products over tiles that
+// choose their expert's matrix, moe_gate_mul_rows, moe_combine): every token passes only through its own experts.
 #include "common.cuh"
 
 namespace ps {
@@ -131,17 +134,131 @@ moe_gate_mul_kernel(const T* __restrict__ gate_up, int gu_stride, const float* _
     dense = pdl_fresh(dense);
     shared_gate = pdl_fresh(shared_gate);
     const long long total = (long long)tokens * columns;
+    const int shared_ff = columns - E * F;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
         const int t = (int)(i / columns), c = (int)(i - (long long)t * columns);
-        const int e = c / F;
+        const int e = c < E * F ? c / F : E;
         const float w = e < E ? dense[(size_t)t * E + e] : shared_gate[t];
         float v = 0.f;
         if (w != 0.f) {
-            const T* row = gate_up + (size_t)t * gu_stride;
-            v = silu(to_float(row[c])) * to_float(row[columns + c]) * w;
+            // an expert's block of the stacked product is its gate columns, then its up columns
+            const int j = c - e * F;
+            const T* block = gate_up + (size_t)t * gu_stride + 2 * (size_t)e * F;
+            v = silu(to_float(block[j])) * to_float(block[(e < E ? F : shared_ff) + j]) * w;
         }
         inner[(size_t)t * inner_stride + c] = from_float<T>(v);
+    }
+}
+
+// ---- rows sorted by expert (steps of many tokens) ----
+// moe_plan, one CTA: every (token, chosen expert) pair gets a row in a buffer in which the rows of one expert lie
+// together and every expert's run starts on a multiple of `tile` rows (the row count of a product's tile), so that a
+// tile of the product belongs to one expert.  row_of[t * top + k]: the pair's row (-1: no expert);
+// row_token[row] / row_weight[row]: the token and the weight of a row (-1 / 0 for the padding between runs);
+// tile_expert[tile]: the expert of a tile of rows, -1 behind the last run.  The order of an expert's rows is
+// whatever the atomics give: no result depends on it, every row is computed by itself.
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* __restrict__ chosen, const float* __restrict__ chosen_w, int pairs, int E, int tile,
+                int rows_cap, int* __restrict__ row_of, int* __restrict__ row_token, float* __restrict__ row_weight,
+                int* __restrict__ tile_expert, int top) {
+    __shared__ int count[MOE_MAX_EXPERTS], start[MOE_MAX_EXPERTS + 1], cursor[MOE_MAX_EXPERTS];
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = cursor[e] = 0;
+    __syncthreads();
+    pdl_prologue();
+    chosen = pdl_fresh(chosen);
+    chosen_w = pdl_fresh(chosen_w);
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int e = chosen[i];
+        if (e >= 0 && e < E) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < E; ++e) {
+            start[e] = at;
+            at += (count[e] + tile - 1) / tile * tile;
+        }
+        start[E] = at;
+    }
+    __syncthreads();
+    for (int r = threadIdx.x; r < rows_cap; r += blockDim.x) {
+        row_token[r] = -1;
+        row_weight[r] = 0.f;
+    }
+    for (int t = threadIdx.x; t < rows_cap / tile; t += blockDim.x) {
+        const int first = t * tile;
+        int expert = -1;
+        for (int e = 0; e < E; ++e)
+            if (first >= start[e] && first < start[e + 1] && count[e] > 0 && first < start[e] + count[e]) expert = e;
+        tile_expert[t] = expert;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+        const int e = chosen[i];
+        int row = -1;
+        if (e >= 0 && e < E) {
+            row = start[e] + atomicAdd(&cursor[e], 1);
+            row_token[row] = i / top;
+            row_weight[row] = chosen_w[i];
+        }
+        row_of[i] = row;
+    }
+}
+
+// rows[r] = x[row_token[r]] (zeros for the padding rows); 16 bytes per thread and turn.
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_gather_kernel(const T* __restrict__ x, int x_stride, const int* __restrict__ row_token, T* __restrict__ rows,
+                  int rows_stride, int W) {
+    pdl_prologue();
+    x = pdl_fresh(x);
+    row_token = pdl_fresh(row_token);
+    const int r = blockIdx.x;
+    const int t = row_token[r];
+    T* dst = rows + (size_t)r * rows_stride;
+    const T* src = x + (size_t)(t < 0 ? 0 : t) * x_stride;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) dst[c] = t < 0 ? from_float<T>(0.f) : src[c];
+}
+
+// inner[r, j] = silu(gate_up[r, j]) * gate_up[r, F + j] * row_weight[r]
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_gate_mul_rows_kernel(const T* __restrict__ gate_up, int gu_stride, const float* __restrict__ row_weight,
+                         T* __restrict__ inner, int inner_stride, int rows, int F) {
+    pdl_prologue();
+    gate_up = pdl_fresh(gate_up);
+    row_weight = pdl_fresh(row_weight);
+    const long long total = (long long)rows * F;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(i / F), j = (int)(i - (long long)r * F);
+        const float w = row_weight[r];
+        float v = 0.f;
+        if (w != 0.f) {
+            const T* row = gate_up + (size_t)r * gu_stride;
+            v = silu(to_float(row[j])) * to_float(row[F + j]) * w;
+        }
+        inner[(size_t)r * inner_stride + j] = from_float<T>(v);
+    }
+}
+
+// y[t] += sum over k (in rising order) of down[row_of[t * top + k]]
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* __restrict__ down, int down_stride, const int* __restrict__ row_of, int top,
+                   float* __restrict__ y, int y_stride, int W) {
+    pdl_prologue();
+    down = pdl_fresh(down);
+    row_of = pdl_fresh(row_of);
+    y = pdl_fresh(y);
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float acc = y[(size_t)t * y_stride + c];
+        for (int k = 0; k < top; ++k) {
+            const int r = row_of[t * top + k];
+            if (r >= 0) acc += down[(size_t)r * down_stride + c];
+        }
+        y[(size_t)t * y_stride + c] = acc;
     }
 }
 
@@ -172,13 +289,13 @@ PS_EXPORT int ps_moe_route(const void* x, int x_stride, const void* router, int 
     return PS_ERR_UNSUPPORTED;
 }
 
-// gate_up [T, 2 * columns] (gates, then ups); dense float32 [T, E]; shared_gate float32 [T] (read for columns
-// from E * F on); inner [T, columns].
+// gate_up [T, 2 * columns] (per expert: gates, then ups); dense float32 [T, E]; shared_gate float32 [T] (read for
+// columns from E * F on); inner [T, columns].
 PS_EXPORT int ps_moe_gate_mul(const void* gate_up, int gu_stride, const float* dense, const float* shared_gate,
                               void* inner, int inner_stride, int T, int columns, int E, int F, int dtype,
                               void* stream) {
     if (T <= 0 || columns <= 0) return PS_OK;
-    if (!gate_up || !dense || !inner || E <= 0 || F <= 0 || columns < E * F) return PS_ERR_BAD_ARGUMENT;
+    if (!gate_up || !inner || E < 0 || (E > 0 && !dense) || F <= 0 || columns < E * F) return PS_ERR_BAD_ARGUMENT;
     if (columns > E * F && !shared_gate) return PS_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
     const long long total = (long long)T * columns;
@@ -192,4 +309,59 @@ PS_EXPORT int ps_moe_gate_mul(const void* gate_up, int gu_stride, const float* d
                               (const __nv_bfloat16*)gate_up, gu_stride, dense, shared_gate, (__nv_bfloat16*)inner,
                               inner_stride, T, columns, E, F);
     return PS_ERR_UNSUPPORTED;
+}
+
+// chosen int32 / chosen_w float32 [T * top]; row_of int32 [T * top]; row_token int32, row_weight float32 [rows_cap];
+// tile_expert int32 [rows_cap / tile]; rows_cap: a multiple of tile, at least T * top + E * (tile - 1).
+PS_EXPORT int ps_moe_plan(const int* chosen, const float* chosen_w, int T, int top, int E, int tile, int rows_cap,
+                          int* row_of, int* row_token, float* row_weight, int* tile_expert, void* stream) {
+    if (T <= 0) return PS_OK;
+    if (!chosen || !chosen_w || !row_of || !row_token || !row_weight || !tile_expert || top <= 0 || E <= 0 || tile <= 0)
+        return PS_ERR_BAD_ARGUMENT;
+    if (E > ps::MOE_MAX_EXPERTS) return PS_ERR_UNSUPPORTED;
+    if (rows_cap % tile || (long long)rows_cap < (long long)T * top + (long long)E * (tile - 1)) return PS_ERR_BAD_ARGUMENT;
+    return ps::launch_pdl(ps::moe_plan_kernel, dim3(1), dim3(1024), 0, (cudaStream_t)stream, chosen, chosen_w, T * top,
+                          E, tile, rows_cap, row_of, row_token, row_weight, tile_expert, top);
+}
+
+// x [T, W] -> rows [R, W] by row_token [R]
+PS_EXPORT int ps_moe_gather(const void* x, int x_stride, const int* row_token, void* rows, int rows_stride, int R,
+                            int W, int dtype, void* stream) {
+    if (R <= 0 || W <= 0) return PS_OK;
+    if (!x || !row_token || !rows) return PS_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == PS_F32)
+        return ps::launch_pdl(ps::moe_gather_kernel<float>, dim3(R), dim3(128), 0, s, (const float*)x, x_stride,
+                              row_token, (float*)rows, rows_stride, W);
+    if (dtype == PS_BF16)
+        return ps::launch_pdl(ps::moe_gather_kernel<__nv_bfloat16>, dim3(R), dim3(128), 0, s, (const __nv_bfloat16*)x,
+                              x_stride, row_token, (__nv_bfloat16*)rows, rows_stride, W);
+    return PS_ERR_UNSUPPORTED;
+}
+
+// gate_up [R, 2 F] (gate columns, then up columns); row_weight float32 [R]; inner [R, F]
+PS_EXPORT int ps_moe_gate_mul_rows(const void* gate_up, int gu_stride, const float* row_weight, void* inner,
+                                   int inner_stride, int R, int F, int dtype, void* stream) {
+    if (R <= 0 || F <= 0) return PS_OK;
+    if (!gate_up || !row_weight || !inner) return PS_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long blocks = ((long long)R * F + 255) / 256;
+    const dim3 grid((unsigned)(blocks < 4736 ? blocks : 4736));
+    if (dtype == PS_F32)
+        return ps::launch_pdl(ps::moe_gate_mul_rows_kernel<float>, grid, dim3(256), 0, s, (const float*)gate_up,
+                              gu_stride, row_weight, (float*)inner, inner_stride, R, F);
+    if (dtype == PS_BF16)
+        return ps::launch_pdl(ps::moe_gate_mul_rows_kernel<__nv_bfloat16>, grid, dim3(256), 0, s,
+                              (const __nv_bfloat16*)gate_up, gu_stride, row_weight, (__nv_bfloat16*)inner, inner_stride,
+                              R, F);
+    return PS_ERR_UNSUPPORTED;
+}
+
+// down float32 [R, W]; row_of int32 [T * top]; y float32 [T, W]
+PS_EXPORT int ps_moe_combine(const float* down, int down_stride, const int* row_of, int top, float* y, int y_stride,
+                             int T, int W, void* stream) {
+    if (T <= 0 || W <= 0) return PS_OK;
+    if (!down || !row_of || !y || top <= 0) return PS_ERR_BAD_ARGUMENT;
+    return ps::launch_pdl(ps::moe_combine_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, down, down_stride, row_of,
+                          top, y, y_stride, W);
 }

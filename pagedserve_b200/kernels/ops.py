@@ -93,6 +93,10 @@ _SIGNATURES = {
         "ps_sigmoid_gate": [_P, _I, _P, _I, _I, _I, _I, _P],
         "ps_moe_route": [_P, _I, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
         "ps_moe_gate_mul": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+        "ps_moe_plan": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P],
+        "ps_moe_gather": [_P, _I, _P, _P, _I, _I, _I, _I, _P],
+        "ps_moe_gate_mul_rows": [_P, _I, _P, _P, _I, _I, _I, _I, _P],
+        "ps_moe_combine": [_P, _I, _P, _I, _P, _I, _I, _I, _P],
         "ps_step_shape": [_I, _P, _P, _P, _I, _I, _I, _I, _P],
         "ps_step_fill": [_I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _L, _P, _I, _I, _I, _I, _P],
         "ps_step_begin": [_P, _P, _P, _P, _P, _P],
@@ -118,6 +122,7 @@ _SIGNATURES = {
         "ps_gemm_tc": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P],
         "ps_gemm_rows_tc": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I,
                             _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "ps_gemm_tc_experts": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P],
         "ps_gemm_tc_qkv": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "ps_prefill_attention_tc": [_P, _I, _I, _P, _I, _P, _L, _L, _L, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I,
                                     _I, _I, _F, _I, _P, _F, _P, _P],
@@ -902,7 +907,8 @@ class Ops:
         (``down[:, :rank]``, unit RMS times ``gain``) and the turned shared key part (``down[:, rank:]``) go into
         the token's place of the layer's single cache plane; the turning part of every query head (the last
         ``turning`` of its ``flat + turning`` numbers in ``q``) is turned into the last ``turning`` of the head's
-        ``rank + turning`` numbers in ``q_out``."""
+        ``rank + turning`` numbers in ``q_out``.  ``inv_freq``: float32 [rot_dims / 2, 2], each frequency as a
+        float and the float nearest to the rest (``RotaryPositions.inv_freq_split``)."""
         T = q.shape[0]
         for name, tensor in (("q", q), ("down", down), ("q_out", q_out)):
             _require(tensor, name, self.dtype)
@@ -914,8 +920,8 @@ class Ops:
             raise KernelError("latent_prepare: widths do not match")
         if rot_dims:
             _require(inv_freq, "inv_freq", torch.float32)
-            if inv_freq.numel() != rot_dims // 2:
-                raise KernelError("latent_prepare: one frequency per pair of turning dimensions")
+            if inv_freq.shape != (rot_dims // 2, 2) or not inv_freq.is_contiguous():
+                raise KernelError("latent_prepare: one (high, low) frequency per pair of turning dimensions")
         pools = write_cache and layer is not None and layer.k_pool is not None
         if pools:
             _require(layer.k_pool, "k_pool", self.dtype)
@@ -970,15 +976,17 @@ class Ops:
                                       int(groups or 0), int(keep or 0), self.code, _stream()), "moe_route")
 
     def moe_gate_mul(self, gate_up, dense, shared_gate, inner, n_experts, expert_ff):
-        """inner[t, c] = silu(gate_up[t, c]) * gate_up[t, C + c] * weight, C = inner.shape[1]; the weight of a
-        column is ``dense[t, c // expert_ff]`` for the experts' columns and ``shared_gate[t]`` from column
-        ``n_experts * expert_ff`` on (csrc/moe.cu)."""
+        """inner[t, c] = silu(gate) * up * weight over the stacked product ``gate_up`` [T, 2 C], C = inner.shape[1]:
+        expert e's block of 2 * expert_ff columns is its gates, then its ups, and the shared expert's block follows;
+        the weight of inner's column c is ``dense[t, c // expert_ff]`` for the experts' columns and
+        ``shared_gate[t]`` from column ``n_experts * expert_ff`` on (csrc/moe.cu).  ``n_experts`` 0: the product of a
+        shared expert alone."""
         T, C = inner.shape
         _require(gate_up, "gate_up", self.dtype)
         _require(inner, "inner", self.dtype)
         _require(dense, "dense", torch.float32)
         if (gate_up.shape != (T, 2 * C) or gate_up.stride(1) != 1 or inner.stride(1) != 1
-                or dense.shape != (T, n_experts) or not dense.is_contiguous()):
+                or (n_experts and (dense.shape != (T, n_experts) or not dense.is_contiguous()))):
             raise KernelError("moe_gate_mul: shapes do not match")
         if shared_gate is not None:
             _require(shared_gate, "shared_gate", torch.float32)
@@ -989,6 +997,95 @@ class Ops:
                                          inner.stride(0), T, C, n_experts, expert_ff, self.code, _stream()),
                "moe_gate_mul")
         return inner
+
+    EXPERT_TILE = 128             # rows of a tile of the tcgen05 product: runs of rows of one expert start on these
+
+    def expert_rows(self, tokens, top, experts):
+        """Rows of the buffer in which (token, expert) pairs are sorted by expert, every expert's run padded to whole
+        tiles: enough for any election."""
+        tile = self.EXPERT_TILE
+        return -(-(tokens * top + experts * (tile - 1)) // tile) * tile
+
+    def moe_plan(self, chosen, chosen_w, experts, row_of, row_token, row_weight, tile_expert):
+        """Sort the (token, chosen expert) pairs of ``chosen`` [T, top] by expert (csrc/moe.cu: moe_plan)."""
+        T, top = chosen.shape
+        rows_cap = row_token.numel()
+        _require(chosen, "chosen", torch.int32)
+        _require(chosen_w, "chosen_w", torch.float32)
+        for name, tensor in (("row_of", row_of), ("row_token", row_token), ("tile_expert", tile_expert)):
+            _require(tensor, name, torch.int32)
+        _require(row_weight, "row_weight", torch.float32)
+        if (row_of.numel() != T * top or row_weight.numel() != rows_cap
+                or tile_expert.numel() != rows_cap // self.EXPERT_TILE or not chosen.is_contiguous()
+                or not chosen_w.is_contiguous()):
+            raise KernelError("moe_plan: shapes do not match")
+        self.launches += 1
+        _check(self.core.ps_moe_plan(_ptr(chosen), _ptr(chosen_w), T, top, experts, self.EXPERT_TILE, rows_cap,
+                                     _ptr(row_of), _ptr(row_token), _ptr(row_weight), _ptr(tile_expert), _stream()),
+               "moe_plan")
+
+    def moe_gather(self, x, row_token, rows):
+        """rows[r] = x[row_token[r]], zeros where row_token[r] < 0."""
+        _require(x, "x", self.dtype)
+        _require(rows, "rows", self.dtype)
+        _require(row_token, "row_token", torch.int32)
+        if rows.shape != (row_token.numel(), x.shape[1]) or x.stride(1) != 1 or rows.stride(1) != 1:
+            raise KernelError("moe_gather: shapes do not match")
+        self.launches += 1
+        _check(self.core.ps_moe_gather(_ptr(x), x.stride(0), _ptr(row_token), _ptr(rows), rows.stride(0),
+                                       rows.shape[0], x.shape[1], self.code, _stream()), "moe_gather")
+        return rows
+
+    def moe_gate_mul_rows(self, gate_up, row_weight, inner):
+        """inner[r, j] = silu(gate_up[r, j]) * gate_up[r, F + j] * row_weight[r]."""
+        R, F = inner.shape
+        _require(gate_up, "gate_up", self.dtype)
+        _require(inner, "inner", self.dtype)
+        _require(row_weight, "row_weight", torch.float32)
+        if gate_up.shape != (R, 2 * F) or row_weight.numel() != R or gate_up.stride(1) != 1 or inner.stride(1) != 1:
+            raise KernelError("moe_gate_mul_rows: shapes do not match")
+        self.launches += 1
+        _check(self.core.ps_moe_gate_mul_rows(_ptr(gate_up), gate_up.stride(0), _ptr(row_weight), _ptr(inner),
+                                              inner.stride(0), R, F, self.code, _stream()), "moe_gate_mul_rows")
+        return inner
+
+    def moe_combine(self, down, row_of, top, y):
+        """y[t] += sum_k down[row_of[t * top + k]] (float32; k in rising order, rows < 0 skipped)."""
+        T, W = y.shape
+        _require(down, "down", torch.float32)
+        _require(y, "y", torch.float32)
+        _require(row_of, "row_of", torch.int32)
+        if down.shape[1] != W or row_of.numel() != T * top or down.stride(1) != 1 or y.stride(1) != 1:
+            raise KernelError("moe_combine: shapes do not match")
+        self.launches += 1
+        _check(self.core.ps_moe_combine(_ptr(down), down.stride(0), _ptr(row_of), top, _ptr(y), y.stride(0), T, W,
+                                        _stream()), "moe_combine")
+        return y
+
+    def linear_experts(self, a, w, out, tile_expert, experts, along_k=False, act=None, status=None):
+        """tcgen05 product of rows sorted by expert: tile t of ``a`` (EXPERT_TILE rows) times the matrix of expert
+        ``tile_expert[t]``, skipped where that is negative.  ``w``: the experts' [N, K] matrices stacked by rows
+        ([experts * N, K]) or, with ``along_k``, side by side ([N, experts * K])."""
+        M, K = a.shape
+        N = out.shape[1]
+        want = (N, experts * K) if along_k else (experts * N, K)
+        if tuple(w.shape) != want or out.shape[0] != M or tile_expert.numel() != -(-M // self.EXPERT_TILE):
+            raise KernelError("linear_experts: shapes do not match")
+        _require(a, "a", torch.bfloat16)
+        _require(w, "w", torch.bfloat16)
+        _require(out, "out")
+        _require(tile_expert, "tile_expert", torch.int32)
+        if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+            raise KernelError("linear_experts: innermost stride must be 1")
+        if self._tc is None:
+            self._tc = _declare(_load_library("tc"), "tc")
+        if status is None:
+            status = self.status_flag(a.device)
+        self.launches += 1
+        _check(self._tc.ps_gemm_tc_experts(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(out), out.stride(0), M, N,
+                                           K, dtype_code(out.dtype), _ACT_CODE[act], _ptr(tile_expert), experts,
+                                           1 if along_k else 0, _ptr(status), _stream()), "gemm_tc_experts")
+        return out
 
     # ------------------------------------------------------------------ sampling
     def sample(self, logits, temperature, seed, position, out, pos_offset=0):

@@ -267,7 +267,7 @@ class LatentAttention(Mixer):
         down = projected[:, self.q_width:self.q_width + self.row]
         gate = projected[:, self.q_width + self.row:]
         queries = ops.empty((tokens, H * self.row), dtype, device)
-        ops.latent_prepare(q, down, self.gain, float(p["eps"]), self.rotary.inv_freq(), self.rotary.params["dims"],
+        ops.latent_prepare(q, down, self.gain, float(p["eps"]), self.rotary.inv_freq_split(), self.rotary.params["dims"],
                            ctx, layer, queries, H, d, r, R, write_cache=p.get("write_cache", True))
         # per head: [T, d] x W_uk(h) -> the first R numbers of the head's attention query
         ops.linear_grouped(q.view(tokens, H, d + r)[:, :, :d].permute(1, 0, 2), self.w_uk_t,

@@ -19,13 +19,19 @@ class RoutedExperts(FeedForward):
     chosen s (+ 1e-20).  A shared expert of the same form (its own inner size) runs for every token, multiplied by
     sigmoid(w_sg . x), one number per token.
 
-    How it runs: the router kernel leaves a dense weight per (token, expert), zero where the expert is not
-    chosen.  The gate and up matrices of all experts (and of the shared one) are stacked into one matrix, as are
-    the down matrices along their inner axis, so a step is two products around one elementwise kernel:
-    inner[t, c] = silu(gate) * up * weight[t, expert of c], then residual += inner W_down_all^T.  Every token
-    passes through every expert's columns, with a zero weight where it was not sent there; what a token gets does
-    not depend on the other tokens of the step.  The weight multiplies the inner activation in float32 before it
-    is rounded, so the down product sums the weighted experts in its float32 accumulator.
+    How it runs.  The gate and up matrices of all experts (and of the shared one) are stacked into one matrix,
+    expert by expert, and the down matrices stand side by side along their inner axis; the weight multiplies the
+    inner activation in float32 before it is rounded.
+    Few tokens (decode steps, short portions; and the float32 path): the router kernel leaves a dense weight per
+    (token, expert), zero where the expert is not chosen, and the step is two products around one elementwise
+    kernel: inner[t, c] = silu(gate) * up * weight[t, expert of c], then residual += inner W_down_all^T.  Every
+    token passes through every expert's columns: the weights stream once, which is what bounds such a step.
+    Many tokens in bfloat16: the (token, expert) pairs are sorted by expert into a buffer in which every expert's
+    run starts on a tile of the tcgen05 product (``moe_plan``, ``moe_gather``); the two products read, per tile of
+    rows, the matrix of that tile's expert (``linear_experts``); ``moe_combine`` adds each token's rows into the
+    residual in the order of its election.  The shared expert runs as two plain products beside them.
+    Either way a token's result does not depend on the other tokens of the step, and both ways compute the same
+    sums up to their order.
 
     params: hidden_size, n_experts, expert_ff, top, groups, group_keep, shared_ff (None: no shared expert),
     init_std, out_init_std; tensors ``router``, ``e<i>.gate / up / down``, ``shared.gate / up / down / sg``.
@@ -67,8 +73,8 @@ class RoutedExperts(FeedForward):
         t = lambda name: tensors[self._n(name)]
         names = self._expert_names()
         self.router = t("router").contiguous()
-        self.w_gate_up = torch.cat([t(name + "gate") for name in names] + [t(name + "up") for name in names],
-                                   dim=0).contiguous()                                  # [2 * columns, W]
+        self.w_gate_up = torch.cat([t(name + which) for name in names for which in ("gate", "up")],
+                                   dim=0).contiguous()           # [2 * columns, W]: per expert its gates, then its ups
         self.w_down = torch.cat([t(name + "down") for name in names], dim=1).contiguous()      # [W, columns]
         self.w_shared_gate = t("shared.sg").reshape(-1).contiguous() if self.params.get("shared_ff") else None
 
@@ -84,8 +90,50 @@ class RoutedExperts(FeedForward):
         shared_gate = ops.empty((tokens,), torch.float32, device) if self.w_shared_gate is not None else None
         ops.moe_route(x, self.router, self.w_shared_gate, dense, chosen, chosen_w, shared_gate, p["top"],
                       p.get("groups") or 0, p.get("group_keep") or 0)
+        F, width = p["expert_ff"], p["hidden_size"]
+        if self._sorted_rows(tokens, x):
+            self._forward_sorted(x, residual, dense, chosen, chosen_w, shared_gate)
+            return
         gate_up = ops.empty((tokens, 2 * self.columns), dtype, device)
         ops.linear(x, self.w_gate_up, None, gate_up)
         inner = ops.empty((tokens, self.columns), dtype, device)
-        ops.moe_gate_mul(gate_up, dense, shared_gate, inner, E, p["expert_ff"])
+        ops.moe_gate_mul(gate_up, dense, shared_gate, inner, E, F)
         ops.linear(inner, self.w_down, None, residual, accumulate=True)
+
+    SORTED_FROM = 128             # tokens of a step from which the rows are sorted by expert
+
+    def _sorted_rows(self, tokens, x):
+        """Whether this step sorts its rows by expert: a rule of shapes alone (the same step always takes the
+        same path).  Below SORTED_FROM tokens the weights of all experts stream once whatever the election; where
+        every expert is chosen there is nothing to save."""
+        p = self.params
+        return (self.env.dtype == torch.bfloat16 and tokens >= self.SORTED_FROM and p["top"] < p["n_experts"]
+                and p["expert_ff"] % 8 == 0 and p["hidden_size"] % 8 == 0 and x.stride(0) % 8 == 0
+                and x.data_ptr() % 16 == 0)
+
+    def _forward_sorted(self, x, residual, dense, chosen, chosen_w, shared_gate):
+        p = self.params
+        ops, dtype, device = self.env.ops, self.env.dtype, residual.device
+        tokens, E, top, F, width = x.shape[0], p["n_experts"], p["top"], p["expert_ff"], p["hidden_size"]
+        rows_cap = ops.expert_rows(tokens, top, E)
+        row_of = ops.empty((tokens * top,), torch.int32, device)
+        row_token = ops.empty((rows_cap,), torch.int32, device)
+        row_weight = ops.empty((rows_cap,), torch.float32, device)
+        tile_expert = ops.empty((rows_cap // ops.EXPERT_TILE,), torch.int32, device)
+        ops.moe_plan(chosen, chosen_w, E, row_of, row_token, row_weight, tile_expert)
+        rows = ops.empty((rows_cap, width), dtype, device)
+        ops.moe_gather(x, row_token, rows)
+        gate_up = ops.empty((rows_cap, 2 * F), dtype, device)
+        ops.linear_experts(rows, self.w_gate_up[:E * 2 * F], gate_up, tile_expert, E)
+        inner = ops.empty((rows_cap, F), dtype, device)
+        ops.moe_gate_mul_rows(gate_up, row_weight, inner)
+        down = ops.empty((rows_cap, width), torch.float32, device)
+        ops.linear_experts(inner, self.w_down[:, :E * F], down, tile_expert, E, along_k=True)
+        ops.moe_combine(down, row_of, top, residual)
+        shared_ff = p.get("shared_ff") or 0
+        if shared_ff:
+            gate_up_shared = ops.empty((tokens, 2 * shared_ff), dtype, device)
+            ops.linear(x, self.w_gate_up[E * 2 * F:], None, gate_up_shared)
+            inner_shared = ops.empty((tokens, shared_ff), dtype, device)
+            ops.moe_gate_mul(gate_up_shared, dense, shared_gate, inner_shared, 0, 1)
+            ops.linear(inner_shared, self.w_down[:, E * F:], None, residual, accumulate=True)

@@ -69,6 +69,20 @@ class RotaryPositions(PositionEncoding):
             self._inv_freq = table.to(torch.float32).to(self.env.device)
         return self._inv_freq
 
+    def inv_freq_split(self):
+        """The frequencies as pairs of floats ``[dims / 2, 2]``: the float nearest to each, and the float nearest
+        to what that one misses (for kernels that form position * frequency to more than one float)."""
+        if getattr(self, "_inv_freq_split", None) is None:
+            import torch
+
+            dims = self.params["dims"]
+            exponent = -2.0 * torch.arange(dims // 2, dtype=torch.float64) / max(dims, 1)
+            table = torch.pow(torch.tensor(float(self.params["base"]), dtype=torch.float64), exponent)
+            high = table.to(torch.float32)
+            low = (table - high.to(torch.float64)).to(torch.float32)
+            self._inv_freq_split = torch.stack([high, low], dim=1).contiguous().to(self.env.device)
+        return self._inv_freq_split
+
     def turn_and_store(self, q, k, v, ctx, layer, n_heads, n_kv_heads, write_cache=True):
         """Turn ``q`` in place; write the turned keys and the values (``v``, or the unturned keys when ``v`` is
         None) into the pages of ``layer``."""

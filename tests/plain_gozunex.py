@@ -146,11 +146,13 @@ def gated_expert(tensors, prefix, h):
     return (silu(h @ t("gate").T) * (h @ t("up").T)) @ t("down").T
 
 
-def route(scores, top, group_count=None, group_keep=None):
+def route(scores, top, group_count=None, group_keep=None, margins=None):
     """scores [T, E] -> (chosen [T, top], weights [T, top]).  With groups: a group's mark is its best score and only
-    experts of the ``group_keep`` best groups stand for election."""
+    experts of the ``group_keep`` best groups stand for election.  ``margins`` (a list) receives, per token, how
+    clear the election was: the smallest relative gap between the last one in and the first one left out."""
     T, E = scores.shape
     allowed = torch.ones_like(scores, dtype=torch.bool)
+    clear = torch.full((T,), float("inf"), dtype=scores.dtype)
     if group_count:
         per = E // group_count
         marks = scores.reshape(T, group_count, per).max(-1).values
@@ -158,17 +160,26 @@ def route(scores, top, group_count=None, group_keep=None):
         group_ok = torch.zeros(T, group_count, dtype=torch.bool)
         group_ok.scatter_(1, kept, True)
         allowed = group_ok[:, :, None].expand(T, group_count, per).reshape(T, E)
-    chosen = scores.masked_fill(~allowed, float("-inf")).topk(top, dim=-1).indices
+        if group_keep < group_count:
+            ranked = marks.sort(-1, descending=True).values
+            clear = torch.minimum(clear, (ranked[:, group_keep - 1] - ranked[:, group_keep]) / ranked[:, group_keep - 1])
+    standing = scores.masked_fill(~allowed, float("-inf"))
+    chosen = standing.topk(top, dim=-1).indices
+    if top < int(allowed.sum(-1).min()):
+        ranked = standing.sort(-1, descending=True).values
+        clear = torch.minimum(clear, (ranked[:, top - 1] - ranked[:, top]) / ranked[:, top - 1])
+    if margins is not None:
+        margins.append(clear)
     picked = scores.gather(1, chosen)
     return chosen, picked / (picked.sum(-1, keepdim=True) + 1e-20)
 
 
-def moe(tensors, prefix, mlp, h):
+def moe(tensors, prefix, mlp, h, margins=None):
     rt = mlp["router"]
     E = rt["experts"]
     scores = torch.softmax(h @ tensors[prefix + "mlp.router"].to(h.dtype).T, dim=-1)
     groups = rt.get("groups") or {}
-    chosen, weights = route(scores, rt["top"], groups.get("count"), groups.get("keep"))
+    chosen, weights = route(scores, rt["top"], groups.get("count"), groups.get("keep"), margins)
     out = torch.zeros_like(h)
     for e in range(E):
         rows, slot = (chosen == e).nonzero(as_tuple=True)
@@ -191,7 +202,7 @@ def layer_runs(config):
     return list(range(loop["start"])) + span * loop["times"] + list(range(loop["stop"], n))
 
 
-def sublayer(tensors, config, index, which, x, positions):
+def sublayer(tensors, config, index, which, x, positions, margins=None):
     layer = config["layers"][index]
     prefix = f"l{index}."
     eps = config["norm"]["eps"]
@@ -201,12 +212,13 @@ def sublayer(tensors, config, index, which, x, positions):
             return latent_attention(tensors, prefix, layer["mixer"], h, positions, eps)
         return wkv_mixer(tensors, prefix, layer["mixer"], h, eps)
     h = rms_norm(x, tensors[prefix + "norm2"].to(x.dtype), eps)
-    return moe(tensors, prefix, layer["mlp"], h)
+    return moe(tensors, prefix, layer["mlp"], h, margins)
 
 
-def forward(tensors, config, tokens, dtype=torch.float64, trace=None):
+def forward(tensors, config, tokens, dtype=torch.float64, trace=None, margins=None):
     """Logits [T, V] of one sequence.  ``trace`` (a list) receives the residual stream after every layer run
-    (the sum of the streams where there are several)."""
+    (the sum of the streams where there are several); ``margins`` (a list) one tensor [T] per routed
+    feed-forward that ran: how clear each token's election of experts was."""
     T = len(tokens)
     positions = torch.arange(T)
     x0 = embed(tensors, config, tokens, dtype)
@@ -219,11 +231,11 @@ def forward(tensors, config, tokens, dtype=torch.float64, trace=None):
             if which == 2 and config["layers"][index].get("mlp") is None:
                 continue
             if streams is None:
-                x = x + sublayer(tensors, config, index, which, x, positions)
+                x = x + sublayer(tensors, config, index, which, x, positions, margins)
                 continue
             t = lambda name: tensors[f"{prefix}hc{which}.{name}"].to(dtype)
             u = sum(t("in")[s] * streams[s] for s in range(S))
-            y = sublayer(tensors, config, index, which, u, positions)
+            y = sublayer(tensors, config, index, which, u, positions, margins)
             mix, out = t("mix"), t("out")
             streams = [sum(mix[s, j] * streams[s] for s in range(S)) + out[j] * y for j in range(S)]
         if trace is not None:
@@ -232,3 +244,103 @@ def forward(tensors, config, tokens, dtype=torch.float64, trace=None):
         x = sum(streams)
     x = rms_norm(x, tensors["final.norm"].to(dtype), config["norm"]["eps"])
     return x @ tensors["embed"].to(dtype).T
+
+
+# ------------------------------------------------------------------------------- configurations and random models
+def experts_entry(experts, top, ff, shared_ff=None, groups=None, keep=None):
+    router = {"experts": experts, "top": top}
+    if groups:
+        router["groups"] = {"count": groups, "keep": keep}
+    entry = {"kind": "moe", "expert": {"ff": ff}, "router": router}
+    if shared_ff:
+        entry["shared"] = {"ff": shared_ff}
+    return entry
+
+
+def latent_layer(heads, dim, rot_dim, vdim, kv_rank, window, mlp=None, rot_dims=None, base=10000.0, scale=None):
+    mixer = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank,
+             "scale": (dim + rot_dim) ** -0.5 if scale is None else scale,
+             "rot": {"base": base, "dims": rot_dim if rot_dims is None else rot_dims}}
+    if window is not None:
+        mixer["mask"] = {"size": window}
+    return {"type": "latent_attention", "mixer": mixer, "mlp": mlp}
+
+
+def wkv_layer(heads, dim, mlp=None):
+    return {"type": "wkv", "mixer": {"heads": heads, "dim": dim}, "mlp": mlp}
+
+
+def make_config(layers, width, vocab, eps=1e-5, streams=None, loop=None, scale=1.0, pair=(61, 5, 3)):
+    config = {"architecture": "Gozunex", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": layers,
+              "embedding": {"scale": scale}}
+    if pair is not None:
+        config["embedding"]["bigram"] = {"buckets": pair[0], "mul_prev": pair[1], "mul_cur": pair[2]}
+    if streams is not None:
+        config["streams"] = streams
+    if loop is not None:
+        config["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return config
+
+
+def random_model(config, seed, rank=8):
+    """Random tensors under the checkpoint's names, rounded to bfloat16 (stored so)."""
+    g = torch.Generator().manual_seed(seed)
+    W, V = config["width"], config["vocab"]
+    out = {}
+
+    def draw(name, shape, std, centre=0.0):
+        values = torch.randn(shape, generator=g) * std
+        if isinstance(centre, torch.Tensor) or centre:
+            values = values + centre
+        out[name] = values.to(torch.bfloat16)
+
+    draw("embed", (V, W), 1.0)
+    pair = config["embedding"].get("bigram")
+    if pair:
+        draw("bigram", (pair["buckets"] + 1, W), 0.7)
+    draw("final.norm", (W,), 0.1, 1.0)
+    S = config.get("streams")
+    for index, layer in enumerate(config["layers"]):
+        p = f"l{index}."
+        m = layer["mixer"]
+        draw(p + "norm1", (W,), 0.1, 1.0)
+        if layer["type"] == "latent_attention":
+            H, d, r, R, dv = m["heads"], m["dim"], m["rot_dim"], m["kv_rank"], m["vdim"]
+            draw(p + "mix.q", (H * (d + r), W), 1.5 * W ** -0.5)
+            draw(p + "mix.dkv", (R + r, W), 1.5 * W ** -0.5)
+            draw(p + "mix.dkv.norm", (R,), 0.1, 1.0)
+            draw(p + "mix.uk", (H * d, R), R ** -0.5)
+            draw(p + "mix.uv", (H * dv, R), R ** -0.5)
+            draw(p + "mix.g", (H * dv, W), 2.0 * W ** -0.5)
+            draw(p + "mix.o", (W, H * dv), (H * dv) ** -0.5)
+        else:
+            H, d = m["heads"], m["dim"]
+            for s in "rkvgw":
+                draw(p + "mix.mu." + s, (W,), 0.3, 0.4)
+            for s in "rkvg":
+                draw(p + "mix." + s, (H * d, W), W ** -0.5)
+            draw(p + "mix.w1", (rank, W), W ** -0.5)
+            draw(p + "mix.w2", (H * d, rank), 0.4)
+            draw(p + "mix.w0", (H * d,), 1.0, -1.5)
+            draw(p + "mix.u", (H, d), 0.4)
+            draw(p + "mix.norm", (H * d,), 0.1, 1.0)
+            draw(p + "mix.o", (W, H * d), (H * d) ** -0.5)
+        mlp = layer.get("mlp")
+        if mlp is not None:
+            draw(p + "norm2", (W,), 0.1, 1.0)
+            E, F = mlp["router"]["experts"], mlp["expert"]["ff"]
+            draw(p + "mlp.router", (E, W), 4.0 * W ** -0.5)
+            names = [(f"e{e}.", F) for e in range(E)]
+            if mlp.get("shared"):
+                names.append(("shared.", mlp["shared"]["ff"]))
+                draw(p + "mlp.shared.sg", (1, W), 2.0 * W ** -0.5)
+            for name, ff in names:
+                draw(p + "mlp." + name + "gate", (ff, W), 1.5 * W ** -0.5)
+                draw(p + "mlp." + name + "up", (ff, W), 1.5 * W ** -0.5)
+                draw(p + "mlp." + name + "down", (W, ff), ff ** -0.5)
+        if S:
+            for which in ((1, 2) if mlp is not None else (1,)):
+                draw(f"{p}hc{which}.in", (S,), 0.3, 0.8)
+                draw(f"{p}hc{which}.out", (S,), 0.3, 0.9)
+                draw(f"{p}hc{which}.mix", (S, S), 0.15, torch.eye(S))
+    return out
