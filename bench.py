@@ -301,16 +301,19 @@ def _run_reference(args, ref):
 
 
 # ---------------------------------------------------------------------------------------------------------
-# --design tefopel: the design's prefill and decode throughput beside GPT-2 of equal size, and its kernels alone
-DESIGN_SIZES = {"w1024": "tefopel-w1024", "w2048": "tefopel-w2048"}      # named sizes of config/tefopel.py
+# --design NAME: the design's prefill and decode throughput beside the closest other model of equal size, and
+# its kernels alone.  Tefopel stands beside GPT-2; Gozunex (windowed attention over a cached latent, wkv layers,
+# routed experts, several residual streams) beside Tefopel (windowed attention, wkv layers, a dense feed-forward).
+DESIGN_SIZES = {"w1024": "w1024", "w2048": "w2048"}      # named sizes of config/tefopel.py and config/gozunex.py
 DESIGN_CONTEXT = 2048
 
 
 def design_arm(args):
-    """Random models at sizes that resemble real layers: Tefopel (three attention layers, then one wkv layer,
-    repeated) and GPT-2 with the same width, depth, heads, inner size and vocabulary.  Per model: tokens/s of a
-    2,048-token prefill step (two prompts of 1,024) and of decode steps at batch 8 and 64 over 512-token
-    prompts.  Then the design's kernels alone beside the like kernels of GPT-2, against the measured peaks."""
+    """Random models at sizes that resemble real layers: the design (three attention layers, then one wkv layer,
+    repeated) and the closest other model with the same width, depth, heads, inner size per token and vocabulary:
+    GPT-2 beside Tefopel, Tefopel beside Gozunex.  Per model: tokens/s of a 2,048-token prefill step (two prompts
+    of 1,024) and of decode steps at batch 8 and 64 over 512-token prompts.  Then the design's kernels alone
+    beside the like kernels of the other model, against the measured peaks."""
     import numpy as np
     import torch
 
@@ -325,12 +328,21 @@ def design_arm(args):
     steps, warmup = min(args.steps, 64), max(args.warmup, 3)
 
     def configs(name):
-        from pagedserve_b200.config import tefopel as sizes
+        from pagedserve_b200.config import gozunex, tefopel
 
-        size = sizes.NAMED_CONFIGS[name]
+        if args.design == "gozunex":
+            # Tefopel of equal size: same width, depth, heads, window and wkv heads; a head as wide as the cached
+            # row's flat + turning parts; a dense feed-forward as wide as what one token uses of the experts
+            size = gozunex.NAMED_CONFIGS["gozunex-" + name]
+            like = tefopel.repeating_config(width=size["width"], heads=size["heads"], head_dim=size["dim"],
+                                            ff=size["top"] * size["ff"] + (size.get("shared_ff") or 0),
+                                            layers=size["layers"], wkv_heads=size["wkv_heads"], window=size["window"],
+                                            vocab=size["vocab"])
+            return size, {"gozunex": gozunex.named_config("gozunex-" + name), "tefopel": like}
+        size = tefopel.NAMED_CONFIGS["tefopel-" + name]
         gpt2 = GPT2Config(n_layer=size["layers"], n_embd=size["width"], n_head=size["heads"], n_inner=size["ff"],
                           vocab_size=size["vocab"], n_positions=DESIGN_CONTEXT)
-        return size, {"tefopel": sizes.named_config(name), "gpt2": gpt2}
+        return size, {"tefopel": tefopel.named_config("tefopel-" + name), "gpt2": gpt2}
 
     def timed(fn):
         torch.cuda.synchronize()
@@ -388,9 +400,39 @@ def design_arm(args):
         size, pair = configs(DESIGN_SIZES[name])
         report["models"][name] = {"size": size, **{kind: measure(config) for kind, config in pair.items()}}
         both = report["models"][name]
-        both["tefopel_over_gpt2"] = {key: both["tefopel"][key] / both["gpt2"][key]
-                                     for key in ("prefill_tok_s", "decode_b8_tok_s", "decode_b64_tok_s")}
-    if args.dtype == "bfloat16" and not args.skip_points:
+        design, like = list(pair)
+        both[f"{design}_over_{like}"] = {key: both[design][key] / both[like][key]
+                                         for key in ("prefill_tok_s", "decode_b8_tok_s", "decode_b64_tok_s")}
+    if args.dtype == "bfloat16" and not args.skip_points and args.design == "gozunex":
+        from pagedserve_b200.config import gozunex
+
+        hbm, tensor = peaks["hbm_gbs"], peaks["bf16_tflops"]
+        kernels = report["kernels"]
+        for name in (args.design_sizes.split(",") if args.design_sizes else DESIGN_SIZES):
+            size = gozunex.NAMED_CONFIGS["gozunex-" + name]
+            H, d, r, R, width = size["heads"], size["dim"], size["rot_dim"], size["kv_rank"], size["width"]
+            row = R + r
+            # attention over the one-plane cache of rows [latent | turning key] beside Tefopel's keys and values
+            like = microbench.time_decode_attention(64, 1024, H, H, d, window=1024, softcap=50.0, sink=True)
+            own = microbench.time_decode_attention(64, 1024, H, 1, row, window=1024, planes=1)
+            kernels[f"decode_attention_{name}"] = {"tefopel": {**like, "frac_hbm": like["gbs"] / hbm},
+                                                   "gozunex": {**own, "frac_hbm": own["gbs"] / hbm}}
+            if row in (64, 128) and d in (64, 128):
+                like = microbench.time_prefill_attention(2, 1024, H, H, d, window=1024, softcap=50.0, sink=True)
+                own = microbench.time_prefill_attention(2, 1024, H, 1, row, window=1024, planes=1)
+                kernels[f"prefill_attention_{name}"] = {"tefopel": {**like, "frac_tensor": like["tflops"] / tensor},
+                                                        "gozunex": {**own, "frac_tensor": own["tflops"] / tensor}}
+            like = microbench.time_cache_write(2048, H, H, d, rot_dims=(d // 4) * 2)
+            own = microbench.time_latent_prepare(2048, H, d, r, R)
+            kernels[f"cache_write_{name}"] = {"tefopel": {"us": like["us"], "gbs": like["gbs"], "frac_hbm": like["gbs"] / hbm},
+                                              "gozunex": {**own, "frac_hbm": own["gbs"] / hbm}}
+            for label, tokens in (("prefill_2048", 2048), ("decode_b64", 64)):
+                run = microbench.time_hyper_step(tokens, width, 2)
+                kernels[f"streams_{label}_{name}"] = {**run, "frac_hbm": run["gbs"] / hbm}
+            run = microbench.time_experts(2048, width, size["experts"], size["top"], size["ff"])
+            kernels[f"experts_2048_tokens_{name}"] = {**run, "frac_tensor": run["tflops"] / tensor,
+                                                      "dense_frac_tensor": run["dense_tflops"] / tensor}
+    elif args.dtype == "bfloat16" and not args.skip_points:
         hbm, tensor = peaks["hbm_gbs"], peaks["bf16_tflops"]
         kernels = report["kernels"]
         for hd in (64, 128):
@@ -433,7 +475,7 @@ def main():
     parser.add_argument("--serving", type=int, default=0, metavar="REQUESTS",
                         help="instead of the decode measurement: this many requests (prompts U[64,1024), outputs "
                              "U[32,256]) through the scheduler, chunked prefill under a 2,048-token budget")
-    parser.add_argument("--design", default=None, choices=("tefopel",),
+    parser.add_argument("--design", default=None, choices=("tefopel", "gozunex"),
                         help="instead of the default workload: prefill and decode throughput of this design at a few "
                              "sizes beside GPT-2 of equal size, and its kernels alone against the measured peaks")
     parser.add_argument("--design-sizes", default=None, help="comma-separated names out of: " + ", ".join(DESIGN_SIZES))

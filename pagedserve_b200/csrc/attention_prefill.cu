@@ -60,7 +60,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
                          const int* __restrict__ q_start, const int* __restrict__ kv_len,
                          const int* __restrict__ block_table, int bt_stride, const int* __restrict__ item_row,
                          int first_item, int n_items, int n_heads, int n_kv_heads, int page_size, int window,
-                         float scale_log2, SoftmaxExtras extras) {
+                         float scale_log2, SoftmaxExtras extras, const int* __restrict__ row_positions,
+                         int rows_per_item) {
     constexpr int RS = HD + 8;                         // padded row, in elements
     constexpr int CH = HD / 8;                         // 16-byte pieces of a row
     constexpr int KS = HD / 16;                        // k steps over the head dim
@@ -76,19 +77,31 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     v_pool = pdl_fresh(v_pool);
     // which (item, query block) is this CTA?
     int block = blockIdx.x, item = -1, qb = 0;
-    for (int i = first_item; i < first_item + n_items; ++i) {
-        int blocks = (q_start[i + 1] - q_start[i] + BQ - 1) / BQ;
-        if (block < blocks) { item = i; qb = blocks - 1 - block; break; }   // late blocks see most keys: first
-        block -= blocks;
+    // Rows of one position (row_positions given): item i is rows_per_item query rows that all stand at position
+    // row_positions[i] and see the same keys: the query heads of one token that share a key head, laid out as
+    // rows.  Otherwise an item is a prompt portion whose rows stand at consecutive positions.
+    const bool one_position = row_positions != nullptr;
+    if (one_position) {
+        const int blocks = (rows_per_item + BQ - 1) / BQ;
+        if (block < n_items * blocks) { item = first_item + block / blocks; qb = block % blocks; }
+    } else {
+        for (int i = first_item; i < first_item + n_items; ++i) {
+            int blocks = (q_start[i + 1] - q_start[i] + BQ - 1) / BQ;
+            if (block < blocks) { item = i; qb = blocks - 1 - block; break; }   // late blocks see most keys: first
+            block -= blocks;
+        }
     }
     if (item < 0) return;
     const int h = blockIdx.y, g = h / (n_heads / n_kv_heads);
     const int tid = threadIdx.x & (GROUP - 1), lane = tid & 31, warp = tid >> 5;   // within the group
-    const int qs = q_start[item], q_len = q_start[item + 1] - qs;
-    const int pos0 = kv_len[item] - q_len + qb * BQ;              // position of the block's first query
+    const int qs = one_position ? item * rows_per_item : q_start[item];
+    const int q_len = one_position ? rows_per_item : q_start[item + 1] - qs;
+    const int step = one_position ? 0 : 1;                        // positions between neighbouring rows
+    // position of the block's first query
+    const int pos0 = one_position ? pdl_fresh(row_positions)[item] : kv_len[item] - q_len + qb * BQ;
     const int rows = min(BQ, q_len - qb * BQ);                    // valid query rows of the block
     const int tok0 = qs + qb * BQ;
-    const int hi = pos0 + rows - 1;                                // last key any row may see
+    const int hi = pos0 + step * (rows - 1);                       // last key any row may see
     const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
     const int kb_first = lo / BKEY, kb_last = hi / BKEY;
     // the item's block-table row: item_row[item] where the table is kept by request slot, else the item itself
@@ -133,7 +146,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
         l_run[0] = l_run[1] = tq == 0 ? 1.f : 0.f;
     }
     const int row0 = warp * 16 + gq, row1 = row0 + 8;            // the two query rows of this thread
-    const int pos_r0 = pos0 + row0, pos_r1 = pos0 + row1;
+    const int pos_r0 = pos0 + step * row0, pos_r1 = pos0 + step * row1;
 
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks)
@@ -161,8 +174,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
         }
         // ---- scale, mask, online softmax
         const int key0 = kb * BKEY;
-        const bool need_mask = (key0 + BKEY - 1 > pos0) || (window > 0 && key0 < pos0 + rows - 1 - window + 1) ||
-                               rows < BQ;
+        const bool need_mask = (key0 + BKEY - 1 > pos0) || (window > 0 && key0 < hi - window + 1) || rows < BQ;
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
         for (int nt = 0; nt < BKEY / 8; ++nt) {
@@ -279,7 +291,8 @@ template <int HD>
 int launch(const void* q, int q_stride, void* out, int out_stride, const void* k_pool, const void* v_pool,
            long long page_stride, const int* q_start, const int* kv_len, const int* block_table, int bt_stride,
            const int* item_row, int first_item, int n_items, int max_blocks, int n_heads, int n_kv_heads,
-           int page_size, int window, float scale, float softcap, const float* sink, cudaStream_t stream) {
+           int page_size, int window, float scale, float softcap, const float* sink, cudaStream_t stream,
+           const int* row_positions = nullptr, int rows_per_item = 0) {
     constexpr int RS = HD + 8;
     size_t smem = (size_t)(BQ + 8 * BKEY) * RS * 2;
     auto kernel = prefill_attention_kernel<HD>;
@@ -288,7 +301,8 @@ int launch(const void* q, int q_stride, void* out, int out_stride, const void* k
     return launch_pdl(kernel, dim3(max_blocks, n_heads), dim3(THREADS), smem, stream, (const __nv_bfloat16*)q, q_stride,
                       (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
                       page_stride, q_start, kv_len, block_table, bt_stride, item_row, first_item, n_items, n_heads,
-                      n_kv_heads, page_size, window, scale * 1.4426950408889634f, softmax_extras(scale, softcap, sink));
+                      n_kv_heads, page_size, window, scale * 1.4426950408889634f, softmax_extras(scale, softcap, sink),
+                      row_positions, rows_per_item);
 }
 
 }  // namespace pf
@@ -319,6 +333,38 @@ PS_EXPORT int ps_prefill_attention(const void* q, int q_stride, void* out, int o
         return ps::pf::launch<D>(q, q_stride, out, out_stride, k_pool, v_pool, page_stride, q_start, kv_len,       \
                                  block_table, bt_stride, item_row, first_item, n_items, max_blocks, n_heads,       \
                                  n_kv_heads, page_size, window, scale, softcap, sink, s);
+    switch (head_dim) {
+        PS_PF_CASE(16) PS_PF_CASE(32) PS_PF_CASE(48) PS_PF_CASE(64)
+        PS_PF_CASE(80) PS_PF_CASE(96) PS_PF_CASE(112) PS_PF_CASE(128)
+    }
+#undef PS_PF_CASE
+    return PS_ERR_UNSUPPORTED;
+}
+
+// Attention of query rows that share a position: item i is rows_per_item rows of q (rows i * rows_per_item ...), all
+// at position row_positions[i] of the request whose block-table row is item_row[i], seeing the keys up to and
+// including that position (inside the window).  This is how the query heads of single tokens run when they all
+// read one key/value head: the heads of a token are the rows (q and out are [items * rows_per_item, head_dim]
+// with the given row strides), so every key is fetched once per token instead of once per head.
+PS_EXPORT int ps_shared_position_attention(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
+                                           const void* v_pool, long long page_stride, const int* row_positions,
+                                           const int* block_table, int bt_stride, const int* item_row, int n_items,
+                                           int rows_per_item, int head_dim, int page_size, int window, float scale,
+                                           void* stream) {
+    if (n_items <= 0 || rows_per_item <= 0) return PS_OK;
+    if (!row_positions || !item_row || !block_table) return PS_ERR_BAD_ARGUMENT;
+    if (head_dim <= 0 || head_dim % 16 != 0 || head_dim > 128) return PS_ERR_UNSUPPORTED;
+    if (page_size <= 0 || page_size > 64 || (page_size & (page_size - 1))) return PS_ERR_UNSUPPORTED;
+    if (q_stride % 8 != 0 || out_stride % 2 != 0 || page_stride % 8 != 0) return PS_ERR_UNSUPPORTED;
+    if (((uintptr_t)q & 15) || ((uintptr_t)out & 3) || ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15))
+        return PS_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int blocks = n_items * ((rows_per_item + ps::pf::BQ - 1) / ps::pf::BQ);
+#define PS_PF_CASE(D)                                                                                              \
+    case D:                                                                                                        \
+        return ps::pf::launch<D>(q, q_stride, out, out_stride, k_pool, v_pool, page_stride, nullptr, nullptr,      \
+                                 block_table, bt_stride, item_row, 0, n_items, blocks, 1, 1, page_size, window,    \
+                                 scale, 0.f, nullptr, s, row_positions, rows_per_item);
     switch (head_dim) {
         PS_PF_CASE(16) PS_PF_CASE(32) PS_PF_CASE(48) PS_PF_CASE(64)
         PS_PF_CASE(80) PS_PF_CASE(96) PS_PF_CASE(112) PS_PF_CASE(128)

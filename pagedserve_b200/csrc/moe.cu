@@ -24,13 +24,41 @@ namespace ps {
 
 constexpr int MOE_MAX_EXPERTS = 256;
 constexpr int MOE_WARPS = 4;
+constexpr int MOE_BATCH = 16;                     // experts whose sums a lane keeps in registers at a time
+
+// eight neighbouring elements as floats: one 16-byte access of bfloat16, two of float32
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = raw;
+}
+__device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
 
 template <typename T>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
 moe_route_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ router, int router_stride,
                  const T* __restrict__ shared_gate_w, float* __restrict__ dense, int* __restrict__ chosen,
                  float* __restrict__ chosen_w, float* __restrict__ shared_gate, int tokens, int W, int E, int top,
-                 int groups, int keep) {
+                 int groups, int keep, int by8) {
     pdl_prologue();
     x = pdl_fresh(x);
     __shared__ float score[MOE_WARPS][MOE_MAX_EXPERTS];
@@ -39,12 +67,41 @@ moe_route_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ ro
     const int t = blockIdx.x * MOE_WARPS + warp;
     if (t >= tokens) return;
     const T* row = x + (size_t)t * x_stride;
-    for (int e = 0; e < E; ++e) {
-        const T* w = router + (size_t)e * router_stride;
-        float acc = 0.f;
-        for (int j = lane; j < W; j += 32) acc = fmaf(to_float(row[j]), to_float(w[j]), acc);
-        acc = warp_sum(acc);
-        if (lane == 0) score[warp][e] = acc;
+    if (by8) {
+        // a lane takes eight neighbouring numbers of the row at a time and keeps the sums of MOE_BATCH experts
+        for (int e0 = 0; e0 < E; e0 += MOE_BATCH) {
+            float acc[MOE_BATCH];
+#pragma unroll
+            for (int b = 0; b < MOE_BATCH; ++b) acc[b] = 0.f;
+            for (int j = 8 * lane; j < W; j += 256) {
+                float xv[8];
+                load8(row + j, xv);
+#pragma unroll
+                for (int b = 0; b < MOE_BATCH; ++b) {
+                    if (e0 + b < E) {
+                        float wv[8];
+                        load8(router + (size_t)(e0 + b) * router_stride + j, wv);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) acc[b] = fmaf(xv[i], wv[i], acc[b]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < MOE_BATCH; ++b) {
+                if (e0 + b < E) {
+                    const float total = warp_sum(acc[b]);
+                    if (lane == 0) score[warp][e0 + b] = total;
+                }
+            }
+        }
+    } else {
+        for (int e = 0; e < E; ++e) {
+            const T* w = router + (size_t)e * router_stride;
+            float acc = 0.f;
+            for (int j = lane; j < W; j += 32) acc = fmaf(to_float(row[j]), to_float(w[j]), acc);
+            acc = warp_sum(acc);
+            if (lane == 0) score[warp][e] = acc;
+        }
     }
     if (shared_gate_w) {
         float acc = 0.f;
@@ -128,13 +185,34 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 moe_gate_mul_kernel(const T* __restrict__ gate_up, int gu_stride, const float* __restrict__ dense,
                     const float* __restrict__ shared_gate, T* __restrict__ inner, int inner_stride, int tokens,
-                    int columns, int E, int F) {
+                    int columns, int E, int F, int by8) {
     pdl_prologue();
     gate_up = pdl_fresh(gate_up);
     dense = pdl_fresh(dense);
     shared_gate = pdl_fresh(shared_gate);
     const long long total = (long long)tokens * columns;
     const int shared_ff = columns - E * F;
+    if (by8) {                                  // eight neighbouring columns (of one expert) per thread and turn
+        const int groups = columns >> 3;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)tokens * groups;
+             i += (long long)gridDim.x * blockDim.x) {
+            const int t = (int)(i / groups), c = (int)(i - (long long)t * groups) << 3;
+            const int e = c < E * F ? c / F : E;
+            const float w = e < E ? dense[(size_t)t * E + e] : shared_gate[t];
+            float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (w != 0.f) {
+                const int j = c - e * F;
+                const T* block = gate_up + (size_t)t * gu_stride + 2 * (size_t)e * F;
+                float g[8], u[8];
+                load8(block + j, g);
+                load8(block + (e < E ? F : shared_ff) + j, u);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v[k] = silu(g[k]) * u[k] * w;
+            }
+            store8(inner + (size_t)t * inner_stride + c, v);
+        }
+        return;
+    }
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
         const int t = (int)(i / columns), c = (int)(i - (long long)t * columns);
@@ -210,7 +288,7 @@ moe_plan_kernel(const int* __restrict__ chosen, const float* __restrict__ chosen
 template <typename T>
 __global__ void __launch_bounds__(128)
 moe_gather_kernel(const T* __restrict__ x, int x_stride, const int* __restrict__ row_token, T* __restrict__ rows,
-                  int rows_stride, int W) {
+                  int rows_stride, int W, int by16) {
     pdl_prologue();
     x = pdl_fresh(x);
     row_token = pdl_fresh(row_token);
@@ -218,6 +296,13 @@ moe_gather_kernel(const T* __restrict__ x, int x_stride, const int* __restrict__
     const int t = row_token[r];
     T* dst = rows + (size_t)r * rows_stride;
     const T* src = x + (size_t)(t < 0 ? 0 : t) * x_stride;
+    if (by16) {                                 // 16 bytes per thread and turn
+        constexpr int PER = 16 / sizeof(T);
+        const uint4 zero = make_uint4(0, 0, 0, 0);
+        for (int c = threadIdx.x * PER; c < W; c += blockDim.x * PER)
+            *reinterpret_cast<uint4*>(dst + c) = t < 0 ? zero : *reinterpret_cast<const uint4*>(src + c);
+        return;
+    }
     for (int c = threadIdx.x; c < W; c += blockDim.x) dst[c] = t < 0 ? from_float<T>(0.f) : src[c];
 }
 
@@ -225,11 +310,30 @@ moe_gather_kernel(const T* __restrict__ x, int x_stride, const int* __restrict__
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_gate_mul_rows_kernel(const T* __restrict__ gate_up, int gu_stride, const float* __restrict__ row_weight,
-                         T* __restrict__ inner, int inner_stride, int rows, int F) {
+                         T* __restrict__ inner, int inner_stride, int rows, int F, int by8) {
     pdl_prologue();
     gate_up = pdl_fresh(gate_up);
     row_weight = pdl_fresh(row_weight);
     const long long total = (long long)rows * F;
+    if (by8) {
+        const int groups = F >> 3;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)rows * groups;
+             i += (long long)gridDim.x * blockDim.x) {
+            const int r = (int)(i / groups), j = (int)(i - (long long)r * groups) << 3;
+            const float w = row_weight[r];
+            float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (w != 0.f) {
+                const T* row = gate_up + (size_t)r * gu_stride;
+                float g[8], u[8];
+                load8(row + j, g);
+                load8(row + F + j, u);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) v[k] = silu(g[k]) * u[k] * w;
+            }
+            store8(inner + (size_t)r * inner_stride + j, v);
+        }
+        return;
+    }
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
         const int r = (int)(i / F), j = (int)(i - (long long)r * F);
@@ -246,12 +350,25 @@ moe_gate_mul_rows_kernel(const T* __restrict__ gate_up, int gu_stride, const flo
 // y[t] += sum over k (in rising order) of down[row_of[t * top + k]]
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ down, int down_stride, const int* __restrict__ row_of, int top,
-                   float* __restrict__ y, int y_stride, int W) {
+                   float* __restrict__ y, int y_stride, int W, int by4) {
     pdl_prologue();
     down = pdl_fresh(down);
     row_of = pdl_fresh(row_of);
     y = pdl_fresh(y);
     const int t = blockIdx.x;
+    if (by4) {
+        for (int c = threadIdx.x * 4; c < W; c += blockDim.x * 4) {
+            float4 acc = *reinterpret_cast<const float4*>(y + (size_t)t * y_stride + c);
+            for (int k = 0; k < top; ++k) {
+                const int r = row_of[t * top + k];
+                if (r < 0) continue;
+                const float4 d = *reinterpret_cast<const float4*>(down + (size_t)r * down_stride + c);
+                acc.x += d.x; acc.y += d.y; acc.z += d.z; acc.w += d.w;
+            }
+            *reinterpret_cast<float4*>(y + (size_t)t * y_stride + c) = acc;
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
         float acc = y[(size_t)t * y_stride + c];
         for (int k = 0; k < top; ++k) {
@@ -277,15 +394,18 @@ PS_EXPORT int ps_moe_route(const void* x, int x_stride, const void* router, int 
     if (E > ps::MOE_MAX_EXPERTS) return PS_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid((T + ps::MOE_WARPS - 1) / ps::MOE_WARPS), block(ps::MOE_WARPS * 32);
+    // rows of the input and of the router in 32-byte units: eight numbers per access
+    const int by8 = W % 8 == 0 && x_stride % 8 == 0 && router_stride % 8 == 0 && !((uintptr_t)x & 31) &&
+                    !((uintptr_t)router & 31);
     if (dtype == PS_F32)
         return ps::launch_pdl(ps::moe_route_kernel<float>, grid, block, 0, s, (const float*)x, x_stride,
                               (const float*)router, router_stride, (const float*)shared_gate_w, dense, chosen,
-                              chosen_w, shared_gate, T, W, E, top, groups, keep);
+                              chosen_w, shared_gate, T, W, E, top, groups, keep, by8);
     if (dtype == PS_BF16)
         return ps::launch_pdl(ps::moe_route_kernel<__nv_bfloat16>, grid, block, 0, s, (const __nv_bfloat16*)x,
                               x_stride, (const __nv_bfloat16*)router, router_stride,
                               (const __nv_bfloat16*)shared_gate_w, dense, chosen, chosen_w, shared_gate, T, W, E, top,
-                              groups, keep);
+                              groups, keep, by8);
     return PS_ERR_UNSUPPORTED;
 }
 
@@ -298,16 +418,18 @@ PS_EXPORT int ps_moe_gate_mul(const void* gate_up, int gu_stride, const float* d
     if (!gate_up || !inner || E < 0 || (E > 0 && !dense) || F <= 0 || columns < E * F) return PS_ERR_BAD_ARGUMENT;
     if (columns > E * F && !shared_gate) return PS_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
-    const long long total = (long long)T * columns;
+    const int by8 = F % 8 == 0 && columns % 8 == 0 && gu_stride % 8 == 0 && inner_stride % 8 == 0 &&
+                    !((uintptr_t)gate_up & 31) && !((uintptr_t)inner & 31);
+    const long long total = (long long)T * (by8 ? columns / 8 : columns);
     const long long blocks = (total + 255) / 256;
     const dim3 grid((unsigned)(blocks < 4736 ? blocks : 4736));
     if (dtype == PS_F32)
         return ps::launch_pdl(ps::moe_gate_mul_kernel<float>, grid, dim3(256), 0, s, (const float*)gate_up, gu_stride,
-                              dense, shared_gate, (float*)inner, inner_stride, T, columns, E, F);
+                              dense, shared_gate, (float*)inner, inner_stride, T, columns, E, F, by8);
     if (dtype == PS_BF16)
         return ps::launch_pdl(ps::moe_gate_mul_kernel<__nv_bfloat16>, grid, dim3(256), 0, s,
                               (const __nv_bfloat16*)gate_up, gu_stride, dense, shared_gate, (__nv_bfloat16*)inner,
-                              inner_stride, T, columns, E, F);
+                              inner_stride, T, columns, E, F, by8);
     return PS_ERR_UNSUPPORTED;
 }
 
@@ -330,12 +452,14 @@ PS_EXPORT int ps_moe_gather(const void* x, int x_stride, const int* row_token, v
     if (R <= 0 || W <= 0) return PS_OK;
     if (!x || !row_token || !rows) return PS_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
+    const int by16 = W % 8 == 0 && x_stride % 8 == 0 && rows_stride % 8 == 0 && !((uintptr_t)x & 15) &&
+                     !((uintptr_t)rows & 15);
     if (dtype == PS_F32)
         return ps::launch_pdl(ps::moe_gather_kernel<float>, dim3(R), dim3(128), 0, s, (const float*)x, x_stride,
-                              row_token, (float*)rows, rows_stride, W);
+                              row_token, (float*)rows, rows_stride, W, by16);
     if (dtype == PS_BF16)
         return ps::launch_pdl(ps::moe_gather_kernel<__nv_bfloat16>, dim3(R), dim3(128), 0, s, (const __nv_bfloat16*)x,
-                              x_stride, row_token, (__nv_bfloat16*)rows, rows_stride, W);
+                              x_stride, row_token, (__nv_bfloat16*)rows, rows_stride, W, by16);
     return PS_ERR_UNSUPPORTED;
 }
 
@@ -345,15 +469,17 @@ PS_EXPORT int ps_moe_gate_mul_rows(const void* gate_up, int gu_stride, const flo
     if (R <= 0 || F <= 0) return PS_OK;
     if (!gate_up || !row_weight || !inner) return PS_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
-    const long long blocks = ((long long)R * F + 255) / 256;
+    const int by8 = F % 8 == 0 && gu_stride % 8 == 0 && inner_stride % 8 == 0 && !((uintptr_t)gate_up & 31) &&
+                    !((uintptr_t)inner & 31);
+    const long long blocks = ((long long)R * (by8 ? F / 8 : F) + 255) / 256;
     const dim3 grid((unsigned)(blocks < 4736 ? blocks : 4736));
     if (dtype == PS_F32)
         return ps::launch_pdl(ps::moe_gate_mul_rows_kernel<float>, grid, dim3(256), 0, s, (const float*)gate_up,
-                              gu_stride, row_weight, (float*)inner, inner_stride, R, F);
+                              gu_stride, row_weight, (float*)inner, inner_stride, R, F, by8);
     if (dtype == PS_BF16)
         return ps::launch_pdl(ps::moe_gate_mul_rows_kernel<__nv_bfloat16>, grid, dim3(256), 0, s,
                               (const __nv_bfloat16*)gate_up, gu_stride, row_weight, (__nv_bfloat16*)inner, inner_stride,
-                              R, F);
+                              R, F, by8);
     return PS_ERR_UNSUPPORTED;
 }
 
@@ -362,6 +488,8 @@ PS_EXPORT int ps_moe_combine(const float* down, int down_stride, const int* row_
                              int T, int W, void* stream) {
     if (T <= 0 || W <= 0) return PS_OK;
     if (!down || !row_of || !y || top <= 0) return PS_ERR_BAD_ARGUMENT;
-    return ps::launch_pdl(ps::moe_combine_kernel, dim3(T), dim3(256), 0, (cudaStream_t)stream, down, down_stride, row_of,
-                          top, y, y_stride, W);
+    const int by4 = W % 4 == 0 && down_stride % 4 == 0 && y_stride % 4 == 0 && !((uintptr_t)down & 15) &&
+                    !((uintptr_t)y & 15);
+    return ps::launch_pdl(ps::moe_combine_kernel, dim3(T), dim3(W >= 1024 ? 256 : 128), 0, (cudaStream_t)stream, down,
+                          down_stride, row_of, top, y, y_stride, W, by4);
 }

@@ -120,24 +120,25 @@ def bench_attention(args):
 
 
 # ------------------------------------------------------------------ kernels as functions (bench.py calls these)
-def _paged_inputs(items, context, kv_heads, head_dim, page, rotate_mb=200):
-    """A pool of random pages with one table row per item; several layers so that repeats miss the L2."""
+def _paged_inputs(items, context, kv_heads, head_dim, page, rotate_mb=200, planes=2):
+    """A pool of random pages with one table row per item; several layers so that repeats miss the L2.
+    ``planes`` 1: a cache whose rows are read as keys and as values."""
     pages_per = -(-context // page)
-    layer_bytes = items * pages_per * page * kv_heads * head_dim * 4
+    layer_bytes = items * pages_per * page * kv_heads * head_dim * 2 * planes
     layers = max(1, min(16, int(rotate_mb * 1e6 // layer_bytes) + 1))
-    pool = torch.randn(items * pages_per + 1, layers, 2, kv_heads, page, head_dim, device="cuda").to(torch.bfloat16)
+    pool = torch.randn(items * pages_per + 1, layers, planes, kv_heads, page, head_dim, device="cuda").to(torch.bfloat16)
     table = torch.randperm(items * pages_per, device="cuda").to(torch.int32).view(items, pages_per)
-    return pool, table, layers, layers * 2 * kv_heads * page * head_dim
+    return pool, table, layers, layers * planes * kv_heads * page * head_dim
 
 
 def time_decode_attention(batch, context, heads, kv_heads, head_dim, page=16, window=None, softcap=None,
-                          sink=False, iters=20):
+                          sink=False, iters=20, planes=2):
     """One decode token per request over ``context`` keys (bfloat16 split-key kernel); GB/s over the K and V
-    bytes a token may see."""
+    bytes a token may see (with one plane: over the rows once)."""
     from pagedserve_b200.kernels.ops import Ops
 
     ops = Ops(torch.bfloat16)
-    pool, table, layers, stride = _paged_inputs(batch, context, kv_heads, head_dim, page)
+    pool, table, layers, stride = _paged_inputs(batch, context, kv_heads, head_dim, page, planes=planes)
     q = torch.randn(batch, heads * head_dim, device="cuda").to(torch.bfloat16)
     out = torch.empty_like(q)
     token_item = torch.arange(batch, dtype=torch.int32, device="cuda")
@@ -147,24 +148,24 @@ def time_decode_attention(batch, context, heads, kv_heads, head_dim, page=16, wi
 
     def run(i):
         layer = i % layers
-        ops.paged_attention_decode(q, out, pool[:, layer, 0], pool[:, layer, 1], stride, token_item, positions, table,
-                                   heads, kv_heads, head_dim, page, window, head_dim ** -0.5, context, status=status,
-                                   softcap=softcap, sink=sinks)
+        ops.paged_attention_decode(q, out, pool[:, layer, 0], pool[:, layer, planes - 1], stride, token_item, positions,
+                                   table, heads, kv_heads, head_dim, page, window, head_dim ** -0.5, context,
+                                   status=status, softcap=softcap, sink=sinks)
 
     seconds = _time(run, iters, graph=True)
     seen = min(context, window) if window else context
-    nbytes = batch * seen * kv_heads * head_dim * 2 * 2
+    nbytes = batch * seen * kv_heads * head_dim * 2 * planes
     return {"us": seconds * 1e6, "gbs": nbytes / seconds / 1e9, "status": int(status.item())}
 
 
 def time_prefill_attention(prompts, prompt_len, heads, kv_heads, head_dim, page=16, window=None, softcap=None,
-                           sink=False, iters=10):
+                           sink=False, iters=10, planes=2):
     """Whole prompts through the tcgen05 prompt kernel (bfloat16, head size 64 or 128); TFLOP/s over the
     products of the keys a query may see."""
     from pagedserve_b200.kernels.ops import Ops
 
     ops = Ops(torch.bfloat16)
-    pool, table, layers, _ = _paged_inputs(prompts, prompt_len, kv_heads, head_dim, page, rotate_mb=0)
+    pool, table, layers, _ = _paged_inputs(prompts, prompt_len, kv_heads, head_dim, page, rotate_mb=0, planes=planes)
     total = prompts * prompt_len
     q = torch.randn(total, heads * head_dim, device="cuda").to(torch.bfloat16)
     out = torch.empty_like(q)
@@ -240,6 +241,114 @@ def time_cache_write(tokens, heads, kv_heads, head_dim, page=16, rot_dims=None, 
     moved = tokens * head_dim * 2 * (2 * heads + 3 * kv_heads)
     return {"us": turned * 1e6, "gbs": moved / turned / 1e9, "plain_write_us": plain * 1e6,
             "plain_write_gbs": tokens * head_dim * 2 * 4 * kv_heads / plain / 1e9}
+
+
+def time_latent_prepare(tokens, heads, flat, turning, rank, page=16, iters=20):
+    """The kernel between the input projection and attention of a latent-attention layer (norm of the latent,
+    turns, cache write); GB/s over what it reads and writes."""
+    from types import SimpleNamespace
+
+    from pagedserve_b200.kernels.ops import Ops
+
+    ops = Ops(torch.bfloat16)
+    row = rank + turning
+    pool, table, _, stride = _paged_inputs(1, tokens, 1, row, page, rotate_mb=0, planes=1)
+    q = torch.randn(tokens, heads * (flat + turning), device="cuda").to(torch.bfloat16)
+    down = torch.randn(tokens, row, device="cuda").to(torch.bfloat16)
+    q_out = torch.empty(tokens, heads * row, dtype=torch.bfloat16, device="cuda")
+    gain = torch.ones(rank, device="cuda")
+    freq = 10000.0 ** (-2.0 * torch.arange(turning // 2, dtype=torch.float64) / max(turning, 1))
+    inv_freq = torch.stack([freq.float(), (freq - freq.float().double()).float()], dim=1).contiguous().cuda()
+    item = torch.zeros(tokens, dtype=torch.int32, device="cuda")
+    layer = SimpleNamespace(k_pool=pool[:, 0, 0], page_stride=stride, page_size=page, block_table=table)
+    ctx = SimpleNamespace(token_slot=item, positions=torch.arange(tokens, dtype=torch.int32, device="cuda"))
+    seconds = _time(lambda i: ops.latent_prepare(q, down, gain, 1e-5, inv_freq, turning, ctx, layer, q_out, heads, flat,
+                                                 turning, rank), iters, graph=True)
+    moved = tokens * 2 * (2 * heads * turning + 2 * row)
+    return {"us": seconds * 1e6, "gbs": moved / seconds / 1e9}
+
+
+def time_hyper_step(tokens, width, streams, iters=20):
+    """One pass over the residual streams (update of a sublayer and the read of the next); GB/s over the streams
+    read and written, the sublayer's row read and zeroed, and the next input written."""
+    from pagedserve_b200.kernels.ops import Ops
+
+    ops = Ops(torch.bfloat16)
+    copies = max(1, int(200e6 // (streams * tokens * width * 4)) + 1)           # rotate past the L2
+    x = torch.randn(copies, streams, tokens, width, device="cuda")
+    y = torch.randn(copies, tokens, width, device="cuda")
+    u = torch.empty(tokens, width, device="cuda")
+    mix = (torch.eye(streams) + 0.1 * torch.randn(streams, streams)).cuda()
+    w_out, w_in = torch.ones(streams, device="cuda"), torch.ones(streams, device="cuda")
+    seconds = _time(lambda i: ops.hyper_step(x[i % copies], y[i % copies], mix, w_out, w_in, u), iters, graph=True)
+    moved = tokens * width * 4 * (2 * streams + 3)
+    return {"us": seconds * 1e6, "gbs": moved / seconds / 1e9}
+
+
+def time_experts(tokens, width, experts, top, ff, iters=10):
+    """The routed part of a feed-forward of ``experts`` experts, rows sorted by expert: router, plan, gather, the
+    two tcgen05 products over expert tiles, gate, combine; beside the two plain tcgen05 products of a dense
+    feed-forward with the same inner size per token (top * ff).  TFLOP/s over the useful products."""
+    from pagedserve_b200.kernels.ops import Ops
+
+    ops = Ops(torch.bfloat16)
+    dev = "cuda"
+    x = torch.randn(tokens, width, device=dev).to(torch.bfloat16)
+    router = (torch.randn(experts, width, device=dev) * 0.05).to(torch.bfloat16)
+    w_gu = (torch.randn(experts * 2 * ff, width, device=dev) * width ** -0.5).to(torch.bfloat16)
+    w_down = (torch.randn(width, experts * ff, device=dev) * ff ** -0.5).to(torch.bfloat16)
+    dense = torch.empty(tokens, experts, device=dev)
+    chosen = torch.empty(tokens, top, dtype=torch.int32, device=dev)
+    chosen_w = torch.empty(tokens, top, device=dev)
+    rows_cap = ops.expert_rows(tokens, top, experts)
+    row_of = torch.empty(tokens * top, dtype=torch.int32, device=dev)
+    row_token = torch.empty(rows_cap, dtype=torch.int32, device=dev)
+    row_weight = torch.empty(rows_cap, device=dev)
+    tile_expert = torch.empty(rows_cap // ops.EXPERT_TILE, dtype=torch.int32, device=dev)
+    rows = torch.empty(rows_cap, width, dtype=torch.bfloat16, device=dev)
+    gate_up = torch.empty(rows_cap, 2 * ff, dtype=torch.bfloat16, device=dev)
+    inner = torch.empty(rows_cap, ff, dtype=torch.bfloat16, device=dev)
+    down = torch.empty(rows_cap, width, device=dev)
+    y = torch.zeros(tokens, width, device=dev)
+    status = ops.status_flag(dev)
+    parts = {}
+
+    def routed(i):
+        ops.moe_route(x, router, None, dense, chosen, chosen_w, None, top, 0, 0)
+        ops.moe_plan(chosen, chosen_w, experts, row_of, row_token, row_weight, tile_expert)
+        ops.moe_gather(x, row_token, rows)
+        ops.linear_experts(rows, w_gu, gate_up, tile_expert, experts)
+        ops.moe_gate_mul_rows(gate_up, row_weight, inner)
+        ops.linear_experts(inner, w_down, down, tile_expert, experts, along_k=True)
+        ops.moe_combine(down, row_of, top, y)
+
+    seconds = _time(routed, iters, graph=True)
+    parts["route_us"] = _time(lambda i: ops.moe_route(x, router, None, dense, chosen, chosen_w, None, top, 0, 0), iters,
+                              graph=True) * 1e6
+    parts["plan_us"] = _time(lambda i: ops.moe_plan(chosen, chosen_w, experts, row_of, row_token, row_weight, tile_expert),
+                             iters, graph=True) * 1e6
+    parts["gather_us"] = _time(lambda i: ops.moe_gather(x, row_token, rows), iters, graph=True) * 1e6
+    parts["gate_up_us"] = _time(lambda i: ops.linear_experts(rows, w_gu, gate_up, tile_expert, experts), iters,
+                                graph=True) * 1e6
+    parts["gate_mul_us"] = _time(lambda i: ops.moe_gate_mul_rows(gate_up, row_weight, inner), iters, graph=True) * 1e6
+    parts["down_us"] = _time(lambda i: ops.linear_experts(inner, w_down, down, tile_expert, experts, along_k=True), iters,
+                             graph=True) * 1e6
+    parts["combine_us"] = _time(lambda i: ops.moe_combine(down, row_of, top, y), iters, graph=True) * 1e6
+    # a dense feed-forward of the same inner size per token: up to 2 * top * ff columns, down from top * ff
+    wide = top * ff
+    w_up_d = (torch.randn(2 * wide, width, device=dev) * width ** -0.5).to(torch.bfloat16)
+    w_down_d = (torch.randn(width, wide, device=dev) * wide ** -0.5).to(torch.bfloat16)
+    up_d = torch.empty(tokens, 2 * wide, dtype=torch.bfloat16, device=dev)
+    inner_d = up_d[:, :wide]
+
+    def plain(i):
+        ops.linear_tc(x, w_up_d, None, up_d, status=status)
+        ops.linear_tc(inner_d, w_down_d, None, y, accumulate=True, status=status)
+
+    plain_seconds = _time(plain, iters, graph=True)
+    flops = 2.0 * tokens * top * (3 * ff) * width
+    return {"us": seconds * 1e6, "tflops": flops / seconds / 1e12, "dense_us": plain_seconds * 1e6,
+            "dense_tflops": flops / plain_seconds / 1e12, "status": int(status.item()), **parts}
 
 
 def main(argv=None):

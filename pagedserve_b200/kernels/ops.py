@@ -115,6 +115,7 @@ _SIGNATURES = {
                                               _F, _I, _I, _P, _P, _P, _P, _P],
         "ps_paged_attention_decode_ex": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I,
                                          _I, _I, _F, _I, _I, _I, _P, _P, _P, _P, _F, _P, _P],
+        "ps_shared_position_attention": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _P],
         "ps_prefill_attention": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F,
                                  _F, _P, _P],
     },
@@ -340,15 +341,18 @@ class Ops:
 
     GROUPED_ROWS = 32             # most rows for which equal products run as one grouped launch
 
-    def linear_grouped(self, a, w, out, act=None, act_from_group=0):
+    def linear_grouped(self, a, w, out, act=None, act_from_group=0, max_rows=None):
         """``out[g] = a[g] @ w[g * cols:(g + 1) * cols].T`` for every group g: ``a`` [G, M, K], ``w`` the stacked
         weights [G * cols, K], ``out`` [G, M, cols]; ``act`` is applied to the groups from ``act_from_group`` on.
-        Few rows in bfloat16 run as one launch of the weight-streaming kernel; everything else as G products."""
+        Few rows in bfloat16 run as one launch of the weight-streaming kernel (up to ``max_rows``, at most 64;
+        default GROUPED_ROWS: large matrices do better as products of their own from there); everything else as G
+        products."""
         groups, M, K = a.shape
         cols = out.shape[2]
         if w.shape != (groups * cols, K) or out.shape[:2] != (groups, M):
             raise KernelError("linear_grouped: shapes do not match")
-        one_launch = (self.dtype == torch.bfloat16 and a.dtype == torch.bfloat16 and M <= self.GROUPED_ROWS
+        one_launch = (self.dtype == torch.bfloat16 and a.dtype == torch.bfloat16
+                      and M <= min(64, max_rows or self.GROUPED_ROWS)
                       and cols % 16 == 0 and K % 8 == 0 and a.stride(2) == 1 and out.stride(2) == 1
                       and w.stride(1) == 1 and a.stride(1) % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
                       and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
@@ -687,6 +691,25 @@ class Ops:
             first_item, n_items, max_blocks, n_heads, n_kv_heads,
             head_dim, page_size, window or 0, scale, float(softcap or 0.0), _ptr(sink), _stream()),
             "prefill_attention")
+        return out
+
+    def shared_position_attention(self, q, out, k_pool, v_pool, page_stride, positions, block_table, token_row,
+                                  heads, head_dim, page_size, window, scale):
+        """Attention of single tokens whose ``heads`` query heads all read one key/value head (bfloat16, head
+        sizes that are multiples of 16 up to 128): the heads of a token are the query rows of one tile, so its
+        keys are fetched once.  ``q`` / ``out`` [T, heads * head_dim]; token t stands at ``positions[t]`` and
+        reads the pages of block-table row ``token_row[t]``."""
+        T = q.shape[0]
+        _require(q, "q", torch.bfloat16)
+        _require(out, "out", torch.bfloat16)
+        if (q.shape[1] != heads * head_dim or out.shape != q.shape or not q.is_contiguous()
+                or not out.is_contiguous()):
+            raise KernelError("shared_position_attention: q and out must be contiguous [T, heads * head_dim]")
+        self.launches += 1
+        _check(self.fast.ps_shared_position_attention(
+            _ptr(q), head_dim, _ptr(out), head_dim, _ptr(k_pool), _ptr(v_pool), page_stride, _ptr(positions),
+            _ptr(block_table), block_table.stride(0), _ptr(token_row), T, heads, head_dim, page_size, window or 0,
+            scale, _stream()), "shared_position_attention")
         return out
 
     @staticmethod

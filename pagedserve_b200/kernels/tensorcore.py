@@ -60,7 +60,15 @@ def attention(ops, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, sc
     long_items = ctx.num_items - ctx.num_short_items
     if long_items and head_dim > 128:
         short_tokens, long_items = ctx.num_tokens, 0
-    if short_tokens:
+    if short_tokens and n_kv_heads == 1 and n_heads >= 4 and head_dim <= 128 and softcap is None and sink is None \
+            and q.is_contiguous() and out.is_contiguous():
+        # Every query head reads the one key/value head: the heads of a token become the query rows of one
+        # tile of the prompt kernel, all at the token's position, and the token's keys are fetched once instead
+        # of once per head (64 tokens x 1,024 keys, 16 heads on a row of 128: 88 us through the split-key kernel).
+        ops.shared_position_attention(q[:short_tokens], out[:short_tokens], layer.k_pool, layer.v_pool,
+                                      layer.page_stride, ctx.positions[:short_tokens], layer.block_table,
+                                      ctx.token_slot[:short_tokens], n_heads, head_dim, layer.page_size, window, scale)
+    elif short_tokens:
         # The splits of a (token, head) pair merge through global memory. (With at most one pair per SM the
         # kernel makes one CTA of six teams per pair instead and merges in shared memory: batch 8, 278 -> 259 us
         # per step. One thread-block cluster per pair, which the kernel also offers, lost to both: co-scheduling

@@ -271,12 +271,12 @@ class LatentAttention(Mixer):
                            ctx, layer, queries, H, d, r, R, write_cache=p.get("write_cache", True))
         # per head: [T, d] x W_uk(h) -> the first R numbers of the head's attention query
         ops.linear_grouped(q.view(tokens, H, d + r)[:, :, :d].permute(1, 0, 2), self.w_uk_t,
-                           queries.view(tokens, H, self.row)[:, :, :R].permute(1, 0, 2))
+                           queries.view(tokens, H, self.row)[:, :, :R].permute(1, 0, 2), max_rows=64)
         context = ops.empty((tokens, H * self.row), dtype, device)
         ops.attention(queries, None, None, context, ctx, layer, H, 1, self.row, p.get("window"), float(p["scale"]),
                       write_cache=False)
         heads = ops.empty((tokens, self.v_width), dtype, device)
         ops.linear_grouped(context.view(tokens, H, self.row)[:, :, :R].permute(1, 0, 2), self.w_uv,
-                           heads.view(tokens, H, dv).permute(1, 0, 2))
+                           heads.view(tokens, H, dv).permute(1, 0, 2), max_rows=64)
         ops.sigmoid_gate(heads, gate)
         ops.linear(heads, self.w_o, None, residual, accumulate=True)
