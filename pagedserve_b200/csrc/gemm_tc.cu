@@ -138,6 +138,15 @@ struct TileExperts {
     int experts;
 };
 
+// Column groups: `groups` products of equal shape in one launch, out[:, g * out_cols + n] = sum_k A[:, g * a_cols + k]
+// W[g * N + n, k] for n < N, k < K: the heads of a layer, each with a small matrix of its own, read from and
+// written into column blocks of two wide row-major matrices.  groups 0: off.
+struct ColumnGroups {
+    int groups;
+    int a_cols;
+    int out_cols;
+};
+
 template <int BN> struct Config {
     static constexpr int STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
     static constexpr int STAGES = BN > 128 ? 4 : (BN >= 96 ? 5 : 6);
@@ -159,7 +168,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                const __grid_constant__ CUtensorMap map_out, const float* __restrict__ bias, TOut* __restrict__ out,
                int ldo, int M, int N, int K, int act, int accumulate, int* __restrict__ status, KvScatter kv,
-               TileExperts ex) {
+               TileExperts ex, ColumnGroups cg) {
     using Cfg = Config<BN>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ unsigned char smem_raw[];
@@ -177,7 +186,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // they happen before the wait and overlap its end.
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM;
-    const int num_tiles = tiles_m * tiles_n;
+    const int per_m = (cg.groups > 0 ? cg.groups : 1) * tiles_n;        // tiles of one block of 128 rows
+    const int num_tiles = tiles_m * per_m;
     const int num_kb = (K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -201,7 +211,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (lane == 0) {
             // the weight tiles of the first stages (of this CTA's first tile) go out before the wait
             // (not where tiles choose their weights by a table that a kernel of this step has just written)
-            const uint32_t early = ((int)blockIdx.x < num_tiles && !ex.tile_expert) ? (uint32_t)min(STAGES, num_kb) : 0u;
+            const uint32_t early = ((int)blockIdx.x < num_tiles && !ex.tile_expert && !cg.groups)
+                                       ? (uint32_t)min(STAGES, num_kb) : 0u;
             for (uint32_t kb = 0; kb < early; ++kb) {
                 const int n0 = ((int)blockIdx.x % tiles_n) * BN;
                 mbar_expect_tx(&full[kb], Cfg::STAGE_BYTES);
@@ -212,8 +223,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile / tiles_n) * BM;
-                int n0 = (tile % tiles_n) * BN, k0 = 0;
+                const int m0 = (tile / per_m) * BM;
+                int n0 = (tile % tiles_n) * BN, k0 = 0, a_k0 = 0;
+                if (cg.groups) {                                 // this tile's group: its columns of A, its rows of W
+                    const int group = (tile % per_m) / tiles_n;
+                    a_k0 = group * cg.a_cols;
+                    n0 += group * N;
+                }
                 if (tile_expert) {
                     const int expert = tile_expert[tile / tiles_n];
                     if (expert < 0) continue;
@@ -228,7 +244,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
                         tma_load_2d(a_dst + BM * BK * 2, &map_w, k0 + kb * BK, n0, &full[s]);
                     }
-                    tma_load_2d(a_dst, &map_a, kb * BK, m0, &full[s]);
+                    tma_load_2d(a_dst, &map_a, a_k0 + kb * BK, m0, &full[s]);
                 }
             }
         } else {
@@ -275,7 +291,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int* tile_expert = pdl_fresh(ex.tile_expert);
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
             if (tile_expert && tile_expert[tile / tiles_n] < 0) { --local; continue; }         // a tile of no expert
-            const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+            const int m0 = (tile / per_m) * BM, n0 = (tile % tiles_n) * BN;
+            const int out_col0 = cg.groups ? ((tile % per_m) / tiles_n) * cg.out_cols : 0;     // the group's columns
             const int buf = local & 1;
             // a q|k|v product whose key and value columns go straight into the pages: where this row's go
             // (offset of page, head 0, position in page, 0), looked up while the tile is still being computed
@@ -397,7 +414,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
                 continue;
             }
-            TOut* orow = out + (size_t)m * ldo;
+            TOut* orow = out + (size_t)m * ldo + out_col0;
 #pragma unroll 1
             for (int c = 32 * team; c < BN; c += 64) {      // the two teams take alternate 32-column chunks
                 uint32_t r[32];
@@ -544,37 +561,45 @@ static int sm_count() {
 template <int BN, typename TOut, bool TMA_OUT>
 int launch_kernel(const CUtensorMap& map_a, const CUtensorMap& map_w, const CUtensorMap& map_out, const float* bias,
                   void* out, int ldo, int M, int N, int K, int act, int accumulate, int* status, const KvScatter& kv,
-                  cudaStream_t stream, const TileExperts& ex) {
+                  cudaStream_t stream, const TileExperts& ex, const ColumnGroups& cg) {
     auto kernel = gemm_tc_kernel<BN, TOut, TMA_OUT>;
     static size_t raised[MAX_DEVICES] = {0};
     if (!ensure_dynamic_smem((const void*)kernel, (size_t)Config<BN>::SMEM, raised)) return PS_ERR_LAUNCH;
-    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * (cg.groups > 0 ? cg.groups : 1);
     const int grid = tiles < sm_count() ? tiles : sm_count();
     return launch_pdl(kernel, dim3(grid), dim3(THREADS), Config<BN>::SMEM, stream, map_a, map_w, map_out, bias,
-                      (TOut*)out, ldo, M, N, K, act, accumulate, status, kv, ex);
+                      (TOut*)out, ldo, M, N, K, act, accumulate, status, kv, ex, cg);
 }
 
 template <int BN, typename TOut>
 int launch(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo, int M, int N, int K,
-           int act, int accumulate, int* status, const KvScatter& kv, cudaStream_t stream, const TileExperts& ex) {
+           int act, int accumulate, int* status, const KvScatter& kv, cudaStream_t stream, const TileExperts& ex,
+           const ColumnGroups& cg) {
     CUtensorMap map_a, map_w, map_out;
-    const int w_rows = ex.tile_expert ? (ex.experts - 1) * ex.rows_per_expert + N : N;
+    const int w_rows = cg.groups ? cg.groups * N : (ex.tile_expert ? (ex.experts - 1) * ex.rows_per_expert + N : N);
     const int w_cols = ex.tile_expert ? (ex.experts - 1) * ex.k_per_expert + K : K;
-    if (!make_map(&map_a, A, M, K, lda, BM) || !make_map(&map_w, W, w_rows, w_cols, ldw, BN)) return PS_ERR_LAUNCH;
+    const int a_cols = cg.groups ? (cg.groups - 1) * cg.a_cols + K : K;
+    if (!make_map(&map_a, A, M, a_cols, lda, BM) || !make_map(&map_w, W, w_rows, w_cols, ldw, BN)) return PS_ERR_LAUNCH;
+    if (cg.groups) {            // every group writes its own block of columns: plain stores with bounds, no TMA boxes
+        map_out = map_a;
+        return launch_kernel<BN, TOut, false>(map_a, map_w, map_out, bias, out, ldo, M, N, K, act, accumulate, status, kv,
+                                              stream, ex, cg);
+    }
     // TMA can write the output when its rows start on 16-byte boundaries
     const bool tma_out = (((uintptr_t)out & 15) == 0) && (((size_t)ldo * sizeof(TOut)) % 16 == 0) &&
                          make_out_map(&map_out, out, M, N, ldo, (int)sizeof(TOut));
     if (tma_out)
-        return launch_kernel<BN, TOut, true>(map_a, map_w, map_out, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream, ex);
+        return launch_kernel<BN, TOut, true>(map_a, map_w, map_out, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream, ex, cg);
     if (kv.k_pool) return PS_ERR_UNSUPPORTED;      // the cache write lives in the TMA-store epilogue only
     map_out = map_a;    // unused
-    return launch_kernel<BN, TOut, false>(map_a, map_w, map_out, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream, ex);
+    return launch_kernel<BN, TOut, false>(map_a, map_w, map_out, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream, ex, cg);
 }
 
 template <typename TOut>
 int pick(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo, int M, int N, int K,
          int act, int accumulate, int* status, int bn, const KvScatter& kv, cudaStream_t stream,
-         const TileExperts& ex = TileExperts{nullptr, 0, 0, 0}) {
+         const TileExperts& ex = TileExperts{nullptr, 0, 0, 0}, const ColumnGroups& cg = ColumnGroups{0, 0, 0}) {
+    if (bn == 0 && cg.groups) bn = N <= 64 ? 64 : (N <= 128 ? 128 : 256);     // small matrices: one tile across
     if (bn == 0) {
         const int tiles_m = (M + BM - 1) / BM;
         // widest tile that still gives the SMs enough tiles (measured on B200: 128 wide wins until the
@@ -603,13 +628,13 @@ int pick(const void* A, int lda, const void* W, int ldw, const float* bias, void
         else if (2 * t128 >= sm_count()) bn = 128;
         else bn = 64;
     }
-    if (bn == 256) return launch<256, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream, ex);
-    if (bn == 192) return launch<192, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream, ex);
-    if (bn == 128) return launch<128, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream, ex);
+    if (bn == 256) return launch<256, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream, ex, cg);
+    if (bn == 192) return launch<192, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream, ex, cg);
+    if (bn == 128) return launch<128, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream, ex, cg);
     if constexpr (sizeof(TOut) == 4) {      // 96 columns are three 32-column groups of float32; bfloat16 groups are 64 wide
-        if (bn == 96) return launch<96, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream, ex);
+        if (bn == 96) return launch<96, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream, ex, cg);
     }
-    if (bn == 64) return launch<64, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream, ex);
+    if (bn == 64) return launch<64, TOut>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, kv, stream, ex, cg);
     return PS_ERR_BAD_ARGUMENT;
 }
 
@@ -621,7 +646,8 @@ int pick(const void* A, int lda, const void* W, int ldw, const float* bias, void
 static int gemm_tc_entry(const void* A, int lda, const void* W, int ldw, const float* bias, void* out, int ldo, int M,
                          int N, int K, int out_dtype, int act, int accumulate, int* status, int bn,
                          const ps::KvScatter& kv, void* stream,
-                         const ps::tc::TileExperts& ex = ps::tc::TileExperts{nullptr, 0, 0, 0}) {
+                         const ps::tc::TileExperts& ex = ps::tc::TileExperts{nullptr, 0, 0, 0},
+                         const ps::tc::ColumnGroups& cg = ps::tc::ColumnGroups{0, 0, 0}) {
     if (M <= 0 || N <= 0) return PS_OK;
     if (!status) return PS_ERR_BAD_ARGUMENT;
     // TMA: 16-byte aligned base, row stride a multiple of 16 bytes
@@ -630,13 +656,14 @@ static int gemm_tc_entry(const void* A, int lda, const void* W, int ldw, const f
     if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return PS_ERR_UNSUPPORTED;
     if (accumulate && out_dtype != PS_F32) return PS_ERR_BAD_ARGUMENT;
     if (ex.tile_expert && ex.k_per_expert % 8 != 0) return PS_ERR_UNSUPPORTED;      // TMA: x in units of 16 bytes
+    if (cg.groups && (cg.a_cols % 8 != 0 || ex.tile_expert || kv.k_pool || bias || accumulate)) return PS_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == PS_F32) {
         if (kv.k_pool) return PS_ERR_UNSUPPORTED;
-        return ps::tc::pick<float>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, bn, kv, s, ex);
+        return ps::tc::pick<float>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, bn, kv, s, ex, cg);
     }
     if (out_dtype == PS_BF16)
-        return ps::tc::pick<__nv_bfloat16>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, bn, kv, s, ex);
+        return ps::tc::pick<__nv_bfloat16>(A, lda, W, ldw, bias, out, ldo, M, N, K, act, accumulate, status, bn, kv, s, ex, cg);
     return PS_ERR_UNSUPPORTED;
 }
 
@@ -658,6 +685,21 @@ PS_EXPORT int ps_gemm_tc_experts(const void* A, int lda, const void* W, int ldw,
     ps::KvScatter none = {};
     ps::tc::TileExperts ex{tile_expert, along_k ? 0 : N, along_k ? K : 0, experts};
     return gemm_tc_entry(A, lda, W, ldw, nullptr, out, ldo, M, N, K, out_dtype, act, 0, status, 0, none, stream, ex);
+}
+
+// `groups` products of equal shape in one launch: group g multiplies the columns [g * a_cols, + K) of A [M, lda]
+// by the rows [g * N, + N) of W [groups * N, K] and writes the columns [g * out_cols, + N) of out [M, ldo].
+// a_cols must be a multiple of 8 (TMA reads start on 16-byte boundaries); what lies beside a group's K columns of
+// A must be finite numbers (it meets zeros).
+PS_EXPORT int ps_gemm_tc_groups(const void* A, int lda, const void* W, int ldw, void* out, int ldo, int M, int N, int K,
+                                int groups, int a_cols, int out_cols, int out_dtype, int* status, void* stream) {
+    if (groups <= 0 || a_cols < K || out_cols < N) return PS_ERR_BAD_ARGUMENT;
+    if ((long long)(groups - 1) * a_cols + K > lda || (long long)(groups - 1) * out_cols + N > ldo) return PS_ERR_BAD_ARGUMENT;
+    ps::KvScatter none = {};
+    ps::tc::TileExperts ex{nullptr, 0, 0, 0};
+    ps::tc::ColumnGroups cg{groups, a_cols, out_cols};
+    return gemm_tc_entry(A, lda, W, ldw, nullptr, out, ldo, M, N, K, out_dtype, PS_ACT_NONE, 0, status, 0, none, stream, ex,
+                         cg);
 }
 
 // The packed q|k|v projection of a step with prompt portions: columns [0, q_width) go to `out` (bfloat16), the

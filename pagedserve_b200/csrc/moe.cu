@@ -1,6 +1,6 @@
 // Routed experts: the router and the gated inner activation.
 //
-// moe_route, one warp per token, float32 throughout:
+// moe_route, one CTA per token, float32 throughout:
 //     z = W_router h                    (E numbers; the operands may be bfloat16, sums are float32)
 //     s = softmax(z) over all E experts
 //     with groups: the experts are `groups` runs of E / groups neighbours; a group's mark is its largest s; only
@@ -61,76 +61,85 @@ moe_route_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ ro
                  int groups, int keep, int by8) {
     pdl_prologue();
     x = pdl_fresh(x);
-    __shared__ float score[MOE_WARPS][MOE_MAX_EXPERTS];
-    __shared__ unsigned char open[MOE_WARPS][MOE_MAX_EXPERTS];
+    // One CTA per token.  The E logits (and the shared gate's, as one more row) are dot products over the row: the
+    // threads of the CTA share the row's columns, so that with eight numbers per thread a row of 1,024 is one round
+    // of loads, all in flight together; partial sums meet in shared memory; warp 0 then holds the election.
+    __shared__ float score[MOE_MAX_EXPERTS + 1];
+    __shared__ float partial[MOE_WARPS][MOE_BATCH];
+    __shared__ unsigned char open[MOE_MAX_EXPERTS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * MOE_WARPS + warp;
-    if (t >= tokens) return;
+    const int t = blockIdx.x;
     const T* row = x + (size_t)t * x_stride;
-    if (by8) {
-        // a lane takes eight neighbouring numbers of the row at a time and keeps the sums of MOE_BATCH experts
-        for (int e0 = 0; e0 < E; e0 += MOE_BATCH) {
-            float acc[MOE_BATCH];
+    const int rows = E + (shared_gate_w ? 1 : 0);
+    for (int e0 = 0; e0 < rows; e0 += MOE_BATCH) {
+        float acc[MOE_BATCH];
 #pragma unroll
-            for (int b = 0; b < MOE_BATCH; ++b) acc[b] = 0.f;
-            for (int j = 8 * lane; j < W; j += 256) {
+        for (int b = 0; b < MOE_BATCH; ++b) acc[b] = 0.f;
+        if (by8) {
+            for (int j = 8 * threadIdx.x; j < W; j += 8 * MOE_WARPS * 32) {
                 float xv[8];
                 load8(row + j, xv);
 #pragma unroll
                 for (int b = 0; b < MOE_BATCH; ++b) {
-                    if (e0 + b < E) {
+                    if (e0 + b < rows) {
+                        const T* w = e0 + b < E ? router + (size_t)(e0 + b) * router_stride : shared_gate_w;
                         float wv[8];
-                        load8(router + (size_t)(e0 + b) * router_stride + j, wv);
+                        load8(w + j, wv);
 #pragma unroll
                         for (int i = 0; i < 8; ++i) acc[b] = fmaf(xv[i], wv[i], acc[b]);
                     }
                 }
             }
+        } else {
+            for (int j = threadIdx.x; j < W; j += MOE_WARPS * 32) {
+                const float xv = to_float(row[j]);
 #pragma unroll
-            for (int b = 0; b < MOE_BATCH; ++b) {
-                if (e0 + b < E) {
-                    const float total = warp_sum(acc[b]);
-                    if (lane == 0) score[warp][e0 + b] = total;
+                for (int b = 0; b < MOE_BATCH; ++b) {
+                    if (e0 + b < rows) {
+                        const T* w = e0 + b < E ? router + (size_t)(e0 + b) * router_stride : shared_gate_w;
+                        acc[b] = fmaf(xv, to_float(w[j]), acc[b]);
+                    }
                 }
             }
         }
-    } else {
-        for (int e = 0; e < E; ++e) {
-            const T* w = router + (size_t)e * router_stride;
-            float acc = 0.f;
-            for (int j = lane; j < W; j += 32) acc = fmaf(to_float(row[j]), to_float(w[j]), acc);
-            acc = warp_sum(acc);
-            if (lane == 0) score[warp][e] = acc;
+#pragma unroll
+        for (int b = 0; b < MOE_BATCH; ++b) {
+            const float total = warp_sum(acc[b]);
+            if (lane == 0) partial[warp][b] = total;
         }
+        __syncthreads();
+        if (threadIdx.x < MOE_BATCH && e0 + threadIdx.x < rows) {
+            float total = 0.f;
+#pragma unroll
+            for (int w = 0; w < MOE_WARPS; ++w) total += partial[w][threadIdx.x];
+            score[e0 + threadIdx.x] = total;
+        }
+        __syncthreads();
     }
-    if (shared_gate_w) {
-        float acc = 0.f;
-        for (int j = lane; j < W; j += 32) acc = fmaf(to_float(row[j]), to_float(shared_gate_w[j]), acc);
-        acc = warp_sum(acc);
-        if (lane == 0) shared_gate[t] = 1.0f / (1.0f + expf(-acc));
-    }
+    if (warp != 0) return;
+    if (shared_gate_w && lane == 0) shared_gate[t] = 1.0f / (1.0f + expf(-score[E]));
     __syncwarp();
     // softmax over all experts
     float top_z = -INFINITY;
-    for (int e = lane; e < E; e += 32) top_z = fmaxf(top_z, score[warp][e]);
+    for (int e = lane; e < E; e += 32) top_z = fmaxf(top_z, score[e]);
     top_z = warp_max(top_z);
     float sum = 0.f;
     for (int e = lane; e < E; e += 32) {
-        const float v = expf(score[warp][e] - top_z);
-        score[warp][e] = v;
+        const float v = expf(score[e] - top_z);
+        score[e] = v;
         sum += v;
     }
     sum = warp_sum(sum);
     const float inv = 1.0f / sum;
     for (int e = lane; e < E; e += 32) {
-        score[warp][e] *= inv;
-        open[warp][e] = 1;
+        score[e] *= inv;
+        open[e] = 1;
         dense[(size_t)t * E + e] = 0.f;
     }
     __syncwarp();
     if (lane == 0) {
-        float* s = score[warp];
-        unsigned char* ok = open[warp];
+        float* s = score;
+        unsigned char* ok = open;
         if (groups > 1 && keep < groups) {
             // close every group but the `keep` best: repeatedly drop the group with the lowest mark
             // (ties: the higher index goes first, so that the lower index wins as in the election below)
@@ -393,7 +402,7 @@ PS_EXPORT int ps_moe_route(const void* x, int x_stride, const void* router, int 
     if (shared_gate_w && !shared_gate) return PS_ERR_BAD_ARGUMENT;
     if (E > ps::MOE_MAX_EXPERTS) return PS_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid((T + ps::MOE_WARPS - 1) / ps::MOE_WARPS), block(ps::MOE_WARPS * 32);
+    const dim3 grid(T), block(ps::MOE_WARPS * 32);
     // rows of the input and of the router in 32-byte units: eight numbers per access
     const int by8 = W % 8 == 0 && x_stride % 8 == 0 && router_stride % 8 == 0 && !((uintptr_t)x & 31) &&
                     !((uintptr_t)router & 31);

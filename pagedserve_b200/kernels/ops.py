@@ -123,6 +123,7 @@ _SIGNATURES = {
         "ps_gemm_tc": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P],
         "ps_gemm_rows_tc": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I,
                             _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "ps_gemm_tc_groups": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
         "ps_gemm_tc_experts": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P],
         "ps_gemm_tc_qkv": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _P, _P, _P, _L, _P, _P, _P, _I, _I, _I, _I, _I, _P],
         "ps_prefill_attention_tc": [_P, _I, _I, _P, _I, _P, _L, _L, _L, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I,
@@ -356,6 +357,8 @@ class Ops:
                       and cols % 16 == 0 and K % 8 == 0 and a.stride(2) == 1 and out.stride(2) == 1
                       and w.stride(1) == 1 and a.stride(1) % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
                       and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+        if not one_launch and act is None and self._column_groups_ok(a, w, out):
+            return self.linear_column_groups(a, w, out)
         if not one_launch:
             for g in range(groups):
                 self.linear(a[g], w[g * cols:(g + 1) * cols], None, out[g], act=act if g >= act_from_group else None)
@@ -367,6 +370,33 @@ class Ops:
                                                 _ptr(out), out.stride(1), out.stride(0), M, cols, groups, K,
                                                 dtype_code(out.dtype), _ACT_CODE[act], act_from_group, _stream()),
                "gemm_skinny_grouped")
+        return out
+
+    def _column_groups_ok(self, a, w, out):
+        """Whether the groups of a grouped product are column blocks of two row-major matrices that the tcgen05
+        kernel can walk in one launch: many rows, bfloat16, and TMA's alignment."""
+        groups, M, K = a.shape
+        return (self.dtype == torch.bfloat16 and a.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+                and M > 64 and groups > 1 and a.stride(2) == 1 and out.stride(2) == 1 and w.is_contiguous()
+                and a.stride(0) >= K and a.stride(0) % 8 == 0 and a.stride(1) % 8 == 0 and K % 8 == 0
+                and a.stride(1) >= (groups - 1) * a.stride(0) + K
+                and out.stride(0) >= out.shape[2] and out.stride(1) >= (groups - 1) * out.stride(0) + out.shape[2]
+                and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+    def linear_column_groups(self, a, w, out, status=None):
+        """The grouped product where group g's rows are the columns ``[g * a.stride(0), + K)`` of one row-major
+        matrix and its results the columns ``[g * out.stride(0), + cols)`` of another (the heads of a layer): one
+        launch of the tcgen05 kernel over (row tile, group) pairs (csrc/gemm_tc.cu: ColumnGroups)."""
+        groups, M, K = a.shape
+        cols = out.shape[2]
+        if self._tc is None:
+            self._tc = _declare(_load_library("tc"), "tc")
+        if status is None:
+            status = self.status_flag(a.device)
+        self.launches += 1
+        _check(self._tc.ps_gemm_tc_groups(_ptr(a), a.stride(1), _ptr(w), w.stride(0), _ptr(out), out.stride(1), M, cols,
+                                          K, groups, a.stride(0), out.stride(0), dtype_code(out.dtype), _ptr(status),
+                                          _stream()), "gemm_tc_groups")
         return out
 
     def linear_tc(self, a, w, bias, out, act=None, accumulate=False, status=None, bn=0):

@@ -51,6 +51,9 @@ def linear(ops, a, w, bias, out, act=None, accumulate=False, status=None):
     return ops.linear_simt(a, w, bias, out, act, accumulate)
 
 
+SHARED_POSITION_FROM = 32      # short tokens of a step from which heads that share a key head run as query rows
+
+
 def attention(ops, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, scale, softcap=None, sink=None):
     """Short entries (fewer than ``ctx.LONG_ENTRY`` tokens: decode tokens, short portions) come first in the
     step's flat batch and go token by token through the split-key kernel; long portions go through the
@@ -60,11 +63,13 @@ def attention(ops, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, sc
     long_items = ctx.num_items - ctx.num_short_items
     if long_items and head_dim > 128:
         short_tokens, long_items = ctx.num_tokens, 0
-    if short_tokens and n_kv_heads == 1 and n_heads >= 4 and head_dim <= 128 and softcap is None and sink is None \
-            and q.is_contiguous() and out.is_contiguous():
+    if short_tokens >= SHARED_POSITION_FROM and n_kv_heads == 1 and n_heads >= 4 and head_dim <= 128 \
+            and softcap is None and sink is None and q.is_contiguous() and out.is_contiguous():
         # Every query head reads the one key/value head: the heads of a token become the query rows of one
         # tile of the prompt kernel, all at the token's position, and the token's keys are fetched once instead
-        # of once per head (64 tokens x 1,024 keys, 16 heads on a row of 128: 88 us through the split-key kernel).
+        # of once per head (64 tokens x 1,024 keys, 16 heads on a row of 128: 88 us through the split-key kernel,
+        # about 65 through this one).  One CTA per token walks all its keys, so a handful of tokens is better off
+        # with the split-key kernel's many CTAs (8 tokens: 16 us per layer more here).
         ops.shared_position_attention(q[:short_tokens], out[:short_tokens], layer.k_pool, layer.v_pool,
                                       layer.page_stride, ctx.positions[:short_tokens], layer.block_table,
                                       ctx.token_slot[:short_tokens], n_heads, head_dim, layer.page_size, window, scale)

@@ -135,5 +135,5 @@ class RoutedExperts(FeedForward):
             gate_up_shared = ops.empty((tokens, 2 * shared_ff), dtype, device)
             ops.linear(x, self.w_gate_up[E * 2 * F:], None, gate_up_shared)
             inner_shared = ops.empty((tokens, shared_ff), dtype, device)
-            ops.moe_gate_mul(gate_up_shared, dense, shared_gate, inner_shared, 0, 1)
+            ops.moe_gate_mul(gate_up_shared, dense, shared_gate, inner_shared, 0, shared_ff)
             ops.linear(inner_shared, self.w_down[:, E * F:], None, residual, accumulate=True)

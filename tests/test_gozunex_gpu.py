@@ -60,7 +60,10 @@ CONFIG_G = plain.make_config(
     [L(2, 32, 16, 64, 48, window=70, mlp=X(4, 4, 32)), W(3, 32, mlp=X(3, 3, 48, shared_ff=64)),
      L(3, 64, 32, 32, 96, window=200, scale=0.05), L(2, 16, 16, 16, 48, window=129, rot_dims=4, mlp=X(2, 2, 72))],
     width=128, vocab=211, eps=1e-6, streams=3, loop=(1, 3, 2), pair=(127, 9, 7))
-CONFIGS = {"g": (CONFIG_G, 7, 4, 16), "a": (CONFIG_A, 1, 8, 16), "b": (CONFIG_B, 2, 4, 16), "c": (CONFIG_C, 3, 6, 8),     # config, seed, rank, page
+# many heads on one cached row (rows of 64 and 128 numbers), with and without a window
+CONFIG_H = plain.make_config([L(8, 16, 16, 24, 48, window=50, mlp=X(4, 2, 16)), L(5, 32, 32, 16, 96, window=None)],
+                             width=64, vocab=83, streams=2)
+CONFIGS = {"h": (CONFIG_H, 8, 4, 16), "g": (CONFIG_G, 7, 4, 16), "a": (CONFIG_A, 1, 8, 16), "b": (CONFIG_B, 2, 4, 16), "c": (CONFIG_C, 3, 6, 8),     # config, seed, rank, page
            "d": (CONFIG_D, 4, 3, 32), "e": (CONFIG_E, 5, 5, 16), "f": (CONFIG_F, 6, 8, 16)}
 
 _FOLDERS, _TENSORS, _LOGITS, _SETTLED = {}, {}, {}, {}
@@ -197,7 +200,7 @@ def test_mixed_batches_reuse_pages_and_slots(which, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["e", "f"])
+@pytest.mark.parametrize("which", ["e", "f", "h"])
 def test_models_of_one_kind_of_layer(which, dtype):
     sequences = sequences_for(which, [70, 3, 131, 29, 64, 1], seed=70)
     check_replay(which, dtype, helpers.trace_whole(sequences), sequences, "whole")
@@ -406,6 +409,65 @@ def test_experts_with_many_tokens(which, count, dtype, tol):
         engine.cache.free("y")
         assert rel_err(residual.cpu()[clear], want[clear]) < tol, (which, index)
     engine.check_status()
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 3e-6), ("bfloat16", 1.2e-2)])
+@pytest.mark.parametrize("which,run", [("h", 0), ("h", 1), ("b", 2), ("a", 0)])
+def test_many_single_tokens_at_once(which, run, dtype, tol):
+    """Forty requests of unequal length each bring one token in the same step (in bfloat16 the heads of a token
+    then run as the query rows of one attention tile): every request's row equals the plain layer's."""
+    engine = build_engine(which, dtype, max_num_seqs=48, num_blocks=400)
+    config, tensors = CONFIGS[which][0], _TENSORS[which]
+    index = plain.layer_runs(config)[run]
+    block, layer = layer_context(engine, run)
+    mixer = config["layers"][index]["mixer"]
+    g = torch.Generator().manual_seed(7)
+    lengths = [int(n) for n in torch.randint(2, 230, (40,), generator=g)]
+    lengths[:4] = [2, 17, 71, 201]
+    rows = [torch.randn(n, config["width"], generator=g, dtype=torch.float64).to(engine.dtype) for n in lengths]
+    want = [plain.latent_attention(tensors, f"l{index}.", mixer, fed.double(), torch.arange(n), config["norm"]["eps"])[-1]
+            for fed, n in zip(rows, lengths)]
+    tokens = [helpers.random_tokens(config["vocab"], n, seed=n) for n in lengths]
+    for first in range(0, 40, 4):                                   # the prompts, four at a time
+        names = list(range(first, first + 4))
+        ctx = make_ctx(engine, [(i, tokens[i][:-1], []) for i in names])
+        host = ctx.host
+        fed = torch.cat([rows[i][:-1] for i in host.requests]).to(DEV).contiguous()
+        block.mixer.forward(fed, torch.zeros(fed.shape, dtype=torch.float32, device=DEV), ctx, layer)
+        engine.cache.commit_many(names)
+    ctx = make_ctx(engine, [(i, tokens[i][-1:], []) for i in range(40)])
+    order = ctx.host.requests
+    fed = torch.stack([rows[i][-1] for i in order]).to(DEV).contiguous()
+    residual = torch.zeros(fed.shape, dtype=torch.float32, device=DEV)
+    block.mixer.forward(fed, residual, ctx, layer)
+    engine.cache.commit_many(list(range(40)))
+    assert rel_err(residual, torch.stack([want[i] for i in order])) < tol
+    engine.check_status()
+
+
+@pytest.mark.parametrize("rows", [65, 128, 333])
+@pytest.mark.parametrize("heads,depth,beside_in,cols,beside_out", [(4, 16, 8, 24, 8), (6, 64, 32, 64, 32),
+                                                                   (16, 96, 32, 64, 0), (3, 8, 0, 136, 8)])
+def test_products_of_many_heads_in_one_launch(rows, heads, depth, beside_in, cols, beside_out):
+    """Per-head products whose inputs and results are column blocks of wide matrices (many rows, bfloat16: one
+    launch of the tcgen05 kernel over row tiles and heads) against float32 products; what lies beside a head's
+    columns stays as it was."""
+    from pagedserve_b200.kernels.ops import Ops
+
+    ops = Ops(torch.bfloat16)
+    g = torch.Generator().manual_seed(rows + heads)
+    a_full = torch.randn(rows, heads * (depth + beside_in), generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(heads * cols, depth, generator=g) * depth ** -0.5).to(torch.bfloat16).to(DEV)
+    out_full = torch.full((rows, heads * (cols + beside_out)), 3.0, dtype=torch.bfloat16, device=DEV)
+    a = a_full.view(rows, heads, depth + beside_in)[:, :, :depth].permute(1, 0, 2)
+    out = out_full.view(rows, heads, cols + beside_out)[:, :, :cols].permute(1, 0, 2)
+    assert ops._column_groups_ok(a, w, out)
+    ops.linear_grouped(a, w, out)
+    want = torch.einsum("hmk,hnk->hmn", a.float(), w.view(heads, cols, depth).float())
+    assert rel_err(out.float(), want.cpu()) < 8e-3
+    if beside_out:
+        assert bool((out_full.view(rows, heads, cols + beside_out)[:, :, cols:] == 3.0).all())
+    assert int(ops.status_flag(DEV).item()) == 0
 
 
 @pytest.mark.parametrize("which", ["a", "b", "c", "d"])
