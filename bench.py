@@ -414,9 +414,16 @@ def design_arm(args):
             row = R + r
             # attention over the one-plane cache of rows [latent | turning key] beside Tefopel's keys and values
             like = microbench.time_decode_attention(64, 1024, H, H, d, window=1024, softcap=50.0, sink=True)
-            own = microbench.time_decode_attention(64, 1024, H, 1, row, window=1024, planes=1)
+            split = microbench.time_decode_attention(64, 1024, H, 1, row, window=1024, planes=1)
             kernels[f"decode_attention_{name}"] = {"tefopel": {**like, "frac_hbm": like["gbs"] / hbm},
-                                                   "gozunex": {**own, "frac_hbm": own["gbs"] / hbm}}
+                                                   "gozunex_split_key": {**split, "frac_hbm": split["gbs"] / hbm}}
+            if row <= 128:          # what the engine runs from 32 single tokens on: the heads as query rows
+                own = microbench.time_shared_position_attention(64, 1024, H, row, window=1024)
+                kernels[f"decode_attention_{name}"]["gozunex"] = {**own, "frac_hbm": own["gbs"] / hbm}
+                few = microbench.time_decode_attention(8, 1024, H, 1, row, window=1024, planes=1)
+                few_like = microbench.time_decode_attention(8, 1024, H, H, d, window=1024, softcap=50.0, sink=True)
+                kernels[f"decode_attention_b8_{name}"] = {"tefopel": {**few_like, "frac_hbm": few_like["gbs"] / hbm},
+                                                          "gozunex": {**few, "frac_hbm": few["gbs"] / hbm}}
             if row in (64, 128) and d in (64, 128):
                 like = microbench.time_prefill_attention(2, 1024, H, H, d, window=1024, softcap=50.0, sink=True)
                 own = microbench.time_prefill_attention(2, 1024, H, 1, row, window=1024, planes=1)

@@ -6,7 +6,7 @@
 //     with groups: the experts are `groups` runs of E / groups neighbours; a group's mark is its largest s; only
 //     experts of the `keep` groups with the largest marks stand for election
 //     the `top` largest s among them are chosen (ties: the lower index), and their weights are s / (sum of the
-//     chosen s + 1e-20)
+//     chosen s + 1e-20); the lanes of one warp hold the scores and run every round together
 //     shared gate: sigmoid(w_sg . h), one number per token (where the layer has a shared expert)
 // Results: dense weights [T, E] (0 where an expert is not chosen), the chosen experts and their weights
 // [T, top], and the shared gate [T].
@@ -54,7 +54,7 @@ __device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(MOE_WARPS * 32)
+__global__ void __launch_bounds__(MOE_WARPS * 32, 8)
 moe_route_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ router, int router_stride,
                  const T* __restrict__ shared_gate_w, float* __restrict__ dense, int* __restrict__ chosen,
                  float* __restrict__ chosen_w, float* __restrict__ shared_gate, int tokens, int W, int E, int top,
@@ -118,75 +118,109 @@ moe_route_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ ro
     }
     if (warp != 0) return;
     if (shared_gate_w && lane == 0) shared_gate[t] = 1.0f / (1.0f + expf(-score[E]));
-    __syncwarp();
-    // softmax over all experts
+    // ---- the election, by the lanes of warp 0 together: lane l holds the experts l, l + 32, ...
+    constexpr int PER_LANE = MOE_MAX_EXPERTS / 32;
+    float mine[PER_LANE];
     float top_z = -INFINITY;
-    for (int e = lane; e < E; e += 32) top_z = fmaxf(top_z, score[e]);
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+        const int e = lane + 32 * i;
+        mine[i] = e < E ? score[e] : -INFINITY;
+        top_z = fmaxf(top_z, mine[i]);
+    }
     top_z = warp_max(top_z);
     float sum = 0.f;
-    for (int e = lane; e < E; e += 32) {
-        const float v = expf(score[e] - top_z);
-        score[e] = v;
-        sum += v;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+        mine[i] = lane + 32 * i < E ? expf(mine[i] - top_z) : 0.f;
+        sum += mine[i];
     }
     sum = warp_sum(sum);
     const float inv = 1.0f / sum;
-    for (int e = lane; e < E; e += 32) {
-        score[e] *= inv;
-        open[e] = 1;
-        dense[(size_t)t * E + e] = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+        const int e = lane + 32 * i;
+        mine[i] = e < E ? mine[i] * inv : -INFINITY;           // the softmax; -inf: no such expert
+        if (e < E) {
+            score[e] = mine[i];
+            open[e] = 1;
+            dense[(size_t)t * E + e] = 0.f;
+        }
     }
     __syncwarp();
-    if (lane == 0) {
-        float* s = score;
-        unsigned char* ok = open;
-        if (groups > 1 && keep < groups) {
-            // close every group but the `keep` best: repeatedly drop the group with the lowest mark
-            // (ties: the higher index goes first, so that the lower index wins as in the election below)
-            const int per = E / groups;
-            for (int drop = 0; drop < groups - keep; ++drop) {
-                int worst = -1;
-                float worst_mark = INFINITY;
-                for (int g = 0; g < groups; ++g) {
-                    if (!ok[g * per]) continue;
-                    float mark = -INFINITY;
-                    for (int j = 0; j < per; ++j) mark = fmaxf(mark, s[g * per + j]);
-                    if (mark <= worst_mark) {
-                        worst_mark = mark;
-                        worst = g;
-                    }
+    if (groups > 1 && keep < groups) {
+        // a group's mark is its largest score; groups - keep times the open group with the lowest mark is closed
+        // (ties: the higher index goes, so that the lower index stays, as in the election below)
+        const int per = E / groups;
+        __shared__ float group_mark[MOE_MAX_EXPERTS];
+        for (int g = lane; g < groups; g += 32) {
+            float m = -INFINITY;
+            for (int j = 0; j < per; ++j) m = fmaxf(m, score[g * per + j]);
+            group_mark[g] = m;
+        }
+        __syncwarp();
+        for (int drop = 0; drop < groups - keep; ++drop) {
+            float worst = INFINITY;
+            int worst_g = -1;
+            for (int g = lane; g < groups; g += 32) {
+                const float m = group_mark[g];
+                if (m <= worst && m != INFINITY) { worst = m; worst_g = g; }      // later (higher) g wins ties
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float other = __shfl_xor_sync(0xffffffffu, worst, o);
+                const int other_g = __shfl_xor_sync(0xffffffffu, worst_g, o);
+                if (other_g >= 0 && (worst_g < 0 || other < worst || (other == worst && other_g > worst_g))) {
+                    worst = other;
+                    worst_g = other_g;
                 }
-                if (worst < 0) break;
-                for (int j = 0; j < per; ++j) ok[worst * per + j] = 0;
+            }
+            if (worst_g < 0) break;
+            if (lane == 0) group_mark[worst_g] = INFINITY;       // closed
+            __syncwarp();
+        }
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i) {
+            const int e = lane + 32 * i;
+            if (e < E && group_mark[e / per] == INFINITY) mine[i] = -INFINITY;
+        }
+    }
+    __shared__ int winner[MOE_MAX_EXPERTS];
+    __shared__ float winner_score[MOE_MAX_EXPERTS];
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int best_e = -1;
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i)
+            if (mine[i] > best) { best = mine[i]; best_e = lane + 32 * i; }       // rising e: the lower index wins ties
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float other = __shfl_xor_sync(0xffffffffu, best, o);
+            const int other_e = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (other_e >= 0 && (best_e < 0 || other > best || (other == best && other_e < best_e))) {
+                best = other;
+                best_e = other_e;
             }
         }
-        float total = 0.f;
-        for (int k = 0; k < top; ++k) {
-            int best = -1;
-            float best_s = -INFINITY;
-            for (int e = 0; e < E; ++e)
-                if (ok[e] && s[e] > best_s) {
-                    best_s = s[e];
-                    best = e;
-                }
-            if (best < 0) {                      // fewer open experts than `top`: the rest get no weight
-                chosen[(size_t)t * top + k] = -1;
-                chosen_w[(size_t)t * top + k] = 0.f;
-                continue;
-            }
-            ok[best] = 0;
-            chosen[(size_t)t * top + k] = best;
-            chosen_w[(size_t)t * top + k] = best_s;
-            total += best_s;
+        // every lane now knows the winner; its owner takes it out of the running
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i)
+            if (best_e == lane + 32 * i) mine[i] = -INFINITY;
+        if (lane == 0) {
+            winner[k] = best_e;                                  // -1: fewer open experts than `top`
+            winner_score[k] = best_e >= 0 ? best : 0.f;
         }
-        const float scale = 1.0f / (total + 1e-20f);
-        for (int k = 0; k < top; ++k) {
-            const int e = chosen[(size_t)t * top + k];
-            if (e < 0) continue;
-            const float w = chosen_w[(size_t)t * top + k] * scale;
-            chosen_w[(size_t)t * top + k] = w;
-            dense[(size_t)t * E + e] = w;
-        }
+        if (best_e >= 0) total += best;
+    }
+    __syncwarp();
+    const float scale = 1.0f / (total + 1e-20f);
+    for (int k = lane; k < top; k += 32) {
+        const int e = winner[k];
+        const float w = winner_score[k] * scale;
+        chosen[(size_t)t * top + k] = e;
+        chosen_w[(size_t)t * top + k] = w;
+        if (e >= 0) dense[(size_t)t * E + e] = w;
     }
 }
 

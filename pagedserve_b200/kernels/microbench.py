@@ -243,6 +243,28 @@ def time_cache_write(tokens, heads, kv_heads, head_dim, page=16, rot_dims=None, 
             "plain_write_gbs": tokens * head_dim * 2 * 4 * kv_heads / plain / 1e9}
 
 
+def time_shared_position_attention(batch, context, heads, head_dim, page=16, window=None, iters=20):
+    """One decode token per request whose ``heads`` query heads all read one cached row of ``head_dim`` numbers
+    (a one-plane cache): the heads run as the query rows of one tile; GB/s over the rows a token may see, once."""
+    from pagedserve_b200.kernels.ops import Ops
+
+    ops = Ops(torch.bfloat16)
+    pool, table, layers, stride = _paged_inputs(batch, context, 1, head_dim, page, planes=1)
+    q = torch.randn(batch, heads * head_dim, device="cuda").to(torch.bfloat16)
+    out = torch.empty_like(q)
+    rows = torch.arange(batch, dtype=torch.int32, device="cuda")
+    positions = torch.full((batch,), context - 1, dtype=torch.int32, device="cuda")
+
+    def run(i):
+        layer = i % layers
+        ops.shared_position_attention(q, out, pool[:, layer, 0], pool[:, layer, 0], stride, positions, table, rows,
+                                      heads, head_dim, page, window, head_dim ** -0.5)
+
+    seconds = _time(run, iters, graph=True)
+    seen = min(context, window) if window else context
+    return {"us": seconds * 1e6, "gbs": batch * seen * head_dim * 2 / seconds / 1e9}
+
+
 def time_latent_prepare(tokens, heads, flat, turning, rank, page=16, iters=20):
     """The kernel between the input projection and attention of a latent-attention layer (norm of the latent,
     turns, cache write); GB/s over what it reads and writes."""
