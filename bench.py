@@ -422,8 +422,11 @@ def design_arm(args):
                 kernels[f"decode_attention_{name}"]["gozunex"] = {**own, "frac_hbm": own["gbs"] / hbm}
                 few = microbench.time_decode_attention(8, 1024, H, 1, row, window=1024, planes=1)
                 few_like = microbench.time_decode_attention(8, 1024, H, H, d, window=1024, softcap=50.0, sink=True)
+                few_rows = microbench.time_shared_position_attention(8, 1024, H, row, window=1024)
                 kernels[f"decode_attention_b8_{name}"] = {"tefopel": {**few_like, "frac_hbm": few_like["gbs"] / hbm},
-                                                          "gozunex": {**few, "frac_hbm": few["gbs"] / hbm}}
+                                                          "gozunex": {**few, "frac_hbm": few["gbs"] / hbm},
+                                                          "gozunex_heads_as_rows": {**few_rows,
+                                                                                    "frac_hbm": few_rows["gbs"] / hbm}}
             if row in (64, 128) and d in (64, 128):
                 like = microbench.time_prefill_attention(2, 1024, H, H, d, window=1024, softcap=50.0, sink=True)
                 own = microbench.time_prefill_attention(2, 1024, H, 1, row, window=1024, planes=1)

@@ -69,7 +69,10 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [BQ][RS]
     const int wg = threadIdx.x >> 7;                                           // warp group 0 / 1
     __nv_bfloat16* k_s = q_s + BQ * RS + wg * (4 * BKEY * RS);                 // this group's [2][BKEY][RS]
-    __nv_bfloat16* v_s = k_s + 2 * BKEY * RS;                                  // this group's [2][BKEY][RS]
+    // (a cache of one plane hands in the same pointer for keys and values: the rows are fetched once and read
+    // from the key buffer for both products)
+    const bool one_plane = k_pool == v_pool;
+    __nv_bfloat16* v_s = one_plane ? k_s : k_s + 2 * BKEY * RS;                // this group's [2][BKEY][RS]
 
     pdl_prologue();
     q = pdl_fresh(q);
@@ -126,7 +129,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
                 off = (long long)page * page_stride + ((long long)g * page_size + (key % page_size)) * HD + piece * 8;
             }
             cp_async16(k_s + (buf * BKEY + r) * RS + piece * 8, k_pool + off, ok);
-            cp_async16(v_s + (buf * BKEY + r) * RS + piece * 8, v_pool + off, ok);
+            if (!one_plane) cp_async16(v_s + (buf * BKEY + r) * RS + piece * 8, v_pool + off, ok);
         }
     };
     if (kb_first + wg <= kb_last) load_kv(kb_first + wg, 0);
@@ -157,6 +160,9 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
         cp_async_commit();
         cp_async_wait<1>();
         group_sync(wg);
+        // a warp whose 16 rows all lie beyond the block's rows (a short portion; the few heads of a token that
+        // stand as rows) only helps to fetch: its products would be issued for nothing
+        if (warp * 16 < rows) {
         // ---- S = Q K^T for 16 rows x 64 keys
         float s[BKEY / 8][4];
 #pragma unroll
@@ -231,6 +237,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
                 mma16816(o[dn], a, b[0], b[1]);
                 mma16816(o[dn + 1], a, b[2], b[3]);
             }
+        }
         }
         group_sync(wg);                                // this buffer is refilled two iterations on
     }

@@ -63,7 +63,7 @@ latent_prepare_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
     if (threadIdx.x == 0) {
         float s = 0.f;
         for (int w = 0; w < (int)(blockDim.x >> 5); ++w) s += red[w];
-        inv_shared = rsqrtf(s / (float)rank + eps);
+        inv_shared = 1.0f / sqrtf(s / (float)rank + eps);
     }
     __syncthreads();
     const float inv = inv_shared;

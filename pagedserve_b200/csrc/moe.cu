@@ -58,9 +58,11 @@ __global__ void __launch_bounds__(MOE_WARPS * 32, 8)
 moe_route_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ router, int router_stride,
                  const T* __restrict__ shared_gate_w, float* __restrict__ dense, int* __restrict__ chosen,
                  float* __restrict__ chosen_w, float* __restrict__ shared_gate, int tokens, int W, int E, int top,
-                 int groups, int keep, int by8) {
+                 int groups, int keep, int by8, const float* __restrict__ raw, int raw_stride,
+                 const float* __restrict__ gain, float eps, T* __restrict__ x_out) {
     pdl_prologue();
     x = pdl_fresh(x);
+    raw = pdl_fresh(raw);
     // One CTA per token.  The E logits (and the shared gate's, as one more row) are dot products over the row: the
     // threads of the CTA share the row's columns, so that with eight numbers per thread a row of 1,024 is one round
     // of loads, all in flight together; partial sums meet in shared memory; warp 0 then holds the election.
@@ -69,6 +71,50 @@ moe_route_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ ro
     __shared__ unsigned char open[MOE_MAX_EXPERTS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
+    if (raw) {
+        // The RMS norm in front, folded in: this CTA norms its token's float32 row (x / sqrt(mean(x^2) + eps) * gain),
+        // leaves the rounded row in x_out for the experts' products, and reads its own numbers back below (every
+        // thread the columns it wrote itself).
+        __shared__ float square[MOE_WARPS];
+        __shared__ float inv_shared;
+        const float* source = raw + (size_t)t * raw_stride;
+        T* target = x_out + (size_t)t * x_stride;
+        float sq = 0.f;
+        if (by8) {
+            for (int j = 8 * threadIdx.x; j < W; j += 8 * MOE_WARPS * 32) {
+                float v[8];
+                load8(source + j, v);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sq = fmaf(v[i], v[i], sq);
+            }
+        } else {
+            for (int j = threadIdx.x; j < W; j += MOE_WARPS * 32) sq = fmaf(source[j], source[j], sq);
+        }
+        sq = warp_sum(sq);
+        if (lane == 0) square[warp] = sq;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float total = 0.f;
+            for (int w = 0; w < MOE_WARPS; ++w) total += square[w];
+            inv_shared = 1.0f / sqrtf(total / (float)W + eps);
+        }
+        __syncthreads();
+        const float inv = inv_shared;
+        if (by8) {
+            for (int j = 8 * threadIdx.x; j < W; j += 8 * MOE_WARPS * 32) {
+                float v[8], g[8];
+                load8(source + j, v);
+                load8(gain + j, g);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = v[i] * inv * g[i];
+                store8(target + j, v);
+            }
+        } else {
+            for (int j = threadIdx.x; j < W; j += MOE_WARPS * 32) target[j] = from_float<T>(source[j] * inv * gain[j]);
+        }
+        __syncthreads();
+        x = pdl_fresh(static_cast<const T*>(x_out));      // (a pointer the compiler cannot tie to the stores above)
+    }
     const T* row = x + (size_t)t * x_stride;
     const int rows = E + (shared_gate_w ? 1 : 0);
     for (int e0 = 0; e0 < rows; e0 += MOE_BATCH) {
@@ -426,10 +472,14 @@ moe_combine_kernel(const float* __restrict__ down, int down_stride, const int* _
 
 // x [T, W] rows of the compute type; router [E, W]; shared_gate_w [W] or null; dense float32 [T, E];
 // chosen int32 [T, top]; chosen_w float32 [T, top]; shared_gate float32 [T] (written only with shared_gate_w).
+// raw (may be null): float32 [T, W] rows whose RMS norm (gain float32 [W], eps) is what the router reads: the normed
+// rows are then written to x (which the experts' products read) instead of being read from it.
 PS_EXPORT int ps_moe_route(const void* x, int x_stride, const void* router, int router_stride,
                            const void* shared_gate_w, float* dense, int* chosen, float* chosen_w, float* shared_gate,
-                           int T, int W, int E, int top, int groups, int keep, int dtype, void* stream) {
+                           int T, int W, int E, int top, int groups, int keep, int dtype, const float* raw,
+                           int raw_stride, const float* gain, float eps, void* stream) {
     if (T <= 0) return PS_OK;
+    if (raw && !gain) return PS_ERR_BAD_ARGUMENT;
     if (W <= 0 || E <= 0 || top <= 0 || top > E || !x || !router || !dense || !chosen || !chosen_w)
         return PS_ERR_BAD_ARGUMENT;
     if (groups < 0 || (groups > 1 && (E % groups || keep <= 0 || keep > groups))) return PS_ERR_BAD_ARGUMENT;
@@ -439,16 +489,18 @@ PS_EXPORT int ps_moe_route(const void* x, int x_stride, const void* router, int 
     const dim3 grid(T), block(ps::MOE_WARPS * 32);
     // rows of the input and of the router in 32-byte units: eight numbers per access
     const int by8 = W % 8 == 0 && x_stride % 8 == 0 && router_stride % 8 == 0 && !((uintptr_t)x & 31) &&
-                    !((uintptr_t)router & 31);
+                    !((uintptr_t)router & 31) && !((uintptr_t)shared_gate_w & 15) &&
+                    (!raw || (raw_stride % 8 == 0 && !((uintptr_t)raw & 31) && !((uintptr_t)gain & 31)));
     if (dtype == PS_F32)
         return ps::launch_pdl(ps::moe_route_kernel<float>, grid, block, 0, s, (const float*)x, x_stride,
                               (const float*)router, router_stride, (const float*)shared_gate_w, dense, chosen,
-                              chosen_w, shared_gate, T, W, E, top, groups, keep, by8);
+                              chosen_w, shared_gate, T, W, E, top, groups, keep, by8, raw, raw_stride, gain, eps,
+                              (float*)const_cast<void*>(x));
     if (dtype == PS_BF16)
         return ps::launch_pdl(ps::moe_route_kernel<__nv_bfloat16>, grid, block, 0, s, (const __nv_bfloat16*)x,
                               x_stride, (const __nv_bfloat16*)router, router_stride,
                               (const __nv_bfloat16*)shared_gate_w, dense, chosen, chosen_w, shared_gate, T, W, E, top,
-                              groups, keep, by8);
+                              groups, keep, by8, raw, raw_stride, gain, eps, (__nv_bfloat16*)const_cast<void*>(x));
     return PS_ERR_UNSUPPORTED;
 }
 

@@ -91,7 +91,7 @@ _SIGNATURES = {
         "ps_latent_prepare": [_P, _I, _P, _I, _P, _F, _P, _I, _P, _P, _P, _I, _P, _L, _I, _P, _I, _I, _I, _I, _I, _I,
                               _I, _P],
         "ps_sigmoid_gate": [_P, _I, _P, _I, _I, _I, _I, _P],
-        "ps_moe_route": [_P, _I, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+        "ps_moe_route": [_P, _I, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _F, _P],
         "ps_moe_gate_mul": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
         "ps_moe_plan": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P],
         "ps_moe_gather": [_P, _I, _P, _P, _I, _I, _I, _I, _P],
@@ -1001,12 +1001,14 @@ class Ops:
         return heads
 
     # ------------------------------------------------------------------ routed experts
-    def moe_route(self, x, router, shared_gate_w, dense, chosen, chosen_w, shared_gate, top, groups, keep):
+    def moe_route(self, x, router, shared_gate_w, dense, chosen, chosen_w, shared_gate, top, groups, keep, norm=None):
         """The router of a layer of experts (csrc/moe.cu): softmax of ``x @ router.T`` in float32, the ``top``
         largest among the experts of the ``keep`` best of ``groups`` groups (0 or 1 groups: all experts stand),
         weights normalised to sum 1.  ``dense`` float32 [T, E] gets the weights (0 where not chosen), ``chosen``
         int32 / ``chosen_w`` float32 [T, top] the election, ``shared_gate`` float32 [T] = sigmoid(x . shared_gate_w)
-        where ``shared_gate_w`` [W] is given."""
+        where ``shared_gate_w`` [W] is given.  ``norm`` = (raw float32 [T, W], gain float32 [W], eps): the kernel
+        first writes the RMS norm of ``raw`` into ``x`` (the rows the experts' products then read) instead of
+        reading ``x``."""
         T, W = x.shape
         E = router.shape[0]
         _require(x, "x", self.dtype)
@@ -1023,10 +1025,20 @@ class Ops:
                 or chosen.shape != (T, top) or chosen_w.shape != (T, top)
                 or not (dense.is_contiguous() and chosen.is_contiguous() and chosen_w.is_contiguous())):
             raise KernelError("moe_route: shapes do not match")
+        raw = gain = None
+        eps = 0.0
+        if norm is not None:
+            raw, gain, eps = norm
+            _require(raw, "raw", torch.float32)
+            _require(gain, "gain", torch.float32)
+            if raw.shape != (T, W) or raw.stride(1) != 1 or gain.numel() != W or not gain.is_contiguous():
+                raise KernelError("moe_route: the rows to norm do not fit")
         self.launches += 1
         _check(self.core.ps_moe_route(_ptr(x), x.stride(0), _ptr(router), router.stride(0), _ptr(shared_gate_w),
                                       _ptr(dense), _ptr(chosen), _ptr(chosen_w), _ptr(shared_gate), T, W, E, top,
-                                      int(groups or 0), int(keep or 0), self.code, _stream()), "moe_route")
+                                      int(groups or 0), int(keep or 0), self.code, _ptr(raw),
+                                      raw.stride(0) if raw is not None else 0, _ptr(gain), float(eps), _stream()),
+               "moe_route")
 
     def moe_gate_mul(self, gate_up, dense, shared_gate, inner, n_experts, expert_ff):
         """inner[t, c] = silu(gate) * up * weight over the stacked product ``gate_up`` [T, 2 C], C = inner.shape[1]:

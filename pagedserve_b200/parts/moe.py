@@ -38,7 +38,7 @@ class RoutedExperts(FeedForward):
     """
 
     graph_safe = True
-    accepts_deferred_norm = False
+    accepts_deferred_norm = True       # an RMS norm in front is computed by the router's kernel
 
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
@@ -81,15 +81,23 @@ class RoutedExperts(FeedForward):
     def forward(self, x, residual, ctx):
         p = self.params
         ops, dtype, device = self.env.ops, self.env.dtype, residual.device
+        norm = None
         if hasattr(x, "materialize"):
-            x = x.materialize()
+            prologue = x.norm.fused_prologue() if hasattr(x.norm, "fused_prologue") else None
+            if (prologue is not None and not prologue.has_mean and prologue.bias is None and x.rows is None
+                    and x.x.dtype == torch.float32 and x.x.stride(1) == 1):
+                # the router's kernel norms the rows on its way and leaves them for the products
+                norm = (x.x, prologue.weight, prologue.eps)
+                x = ops.empty(x.shape, dtype, device)
+            else:
+                x = x.materialize()
         tokens, E = x.shape[0], p["n_experts"]
         dense = ops.empty((tokens, E), torch.float32, device)
         chosen = ops.empty((tokens, p["top"]), torch.int32, device)
         chosen_w = ops.empty((tokens, p["top"]), torch.float32, device)
         shared_gate = ops.empty((tokens,), torch.float32, device) if self.w_shared_gate is not None else None
         ops.moe_route(x, self.router, self.w_shared_gate, dense, chosen, chosen_w, shared_gate, p["top"],
-                      p.get("groups") or 0, p.get("group_keep") or 0)
+                      p.get("groups") or 0, p.get("group_keep") or 0, norm=norm)
         F, width = p["expert_ff"], p["hidden_size"]
         if self._sorted_rows(tokens, x):
             self._forward_sorted(x, residual, dense, chosen, chosen_w, shared_gate)

@@ -102,12 +102,21 @@ def plain_logits(which, sequences):
 
 
 def assert_rows_close(got, want, dtype, what, mean_factor=1.0):
-    """float32: every logit within 2e-5 of the scale (sums differ in order only).  bfloat16: a row's error is taken
+    """float32: every logit within 4e-5 of the scale (sums differ in order only; measured up to 2.1e-5 on the models
+    with three streams and repeated layers, 1e-6 on the plain ones), the best token the same.  bfloat16: a row's error is taken
     as the root mean square over the vocabulary against the root mean square of the logits.  Measured on these
     models: 0.3 % to 1.4 % in the mean over the rows and up to 9 % at single rows (several streams and repeated
     layers carry the rounding of every sublayer along); a wrong key, state or expert moves a row by 30 % and more."""
     if dtype == "float32":
-        return helpers.assert_close(got, want, dtype, what)
+        scale = float(np.abs(want).max())
+        error = np.abs(got.astype(np.float64) - want).max(-1)
+        assert got.shape == want.shape and np.isfinite(got).all(), what
+        assert float(error.max()) <= 4e-5 * scale, \
+            f"{what}: row {int(error.argmax())} is off by {float(error.max()):.3e}, scale {scale:.3e}"
+        ordered = np.sort(want, axis=-1)
+        clear = (ordered[:, -1] - ordered[:, -2]) > 1e-4 * scale
+        assert (got.argmax(-1) == want.argmax(-1))[clear].all(), f"{what}: another best token"
+        return
     assert got.shape == want.shape and np.isfinite(got).all(), what
     error = np.sqrt(((got - want) ** 2).mean(-1)) / np.sqrt((want ** 2).mean())
     assert float(error.max()) < 0.15, f"{what}: row {int(error.argmax())} is off by {float(error.max()):.3f}"
