@@ -51,7 +51,7 @@ def linear(ops, a, w, bias, out, act=None, accumulate=False, status=None):
     return ops.linear_simt(a, w, bias, out, act, accumulate)
 
 
-SHARED_POSITION_FROM = 32      # short tokens of a step from which heads that share a key head run as query rows
+SHARED_POSITION_FROM = 40      # short tokens of a step from which heads that share a key head run as query rows
 
 
 def attention(ops, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, scale, softcap=None, sink=None):
@@ -68,8 +68,9 @@ def attention(ops, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, sc
         # Every query head reads the one key/value head: the heads of a token become the query rows of one
         # tile of the prompt kernel, all at the token's position, and the token's keys are fetched once instead
         # of once per head (64 tokens x 1,024 keys, 16 heads on a row of 128: 88 us through the split-key kernel,
-        # about 65 through this one).  One CTA per token walks all its keys, so a handful of tokens is better off
-        # with the split-key kernel's many CTAs (8 tokens: 16 us per layer more here).
+        # 51 through this one).  One CTA per token walks all its keys in turn, which takes those 50 us whatever
+        # the number of tokens, so fewer tokens are better off with the split-key kernel's many CTAs (8 tokens:
+        # 17 us there); the two meet near 37 tokens.
         ops.shared_position_attention(q[:short_tokens], out[:short_tokens], layer.k_pool, layer.v_pool,
                                       layer.page_stride, ctx.positions[:short_tokens], layer.block_table,
                                       ctx.token_slot[:short_tokens], n_heads, head_dim, layer.page_size, window, scale)
