@@ -63,7 +63,12 @@ CONFIG_G = plain.make_config(
 # many heads on one cached row (rows of 64 and 128 numbers), with and without a window
 CONFIG_H = plain.make_config([L(8, 16, 16, 24, 48, window=50, mlp=X(4, 2, 16)), L(5, 32, 32, 16, 96, window=None)],
                              width=64, vocab=83, streams=2)
-CONFIGS = {"h": (CONFIG_H, 8, 4, 16), "g": (CONFIG_G, 7, 4, 16), "a": (CONFIG_A, 1, 8, 16), "b": (CONFIG_B, 2, 4, 16), "c": (CONFIG_C, 3, 6, 8),     # config, seed, rank, page
+# nothing a multiple of 8: width 52, heads of 10 + 4 (per-head views that start on odd boundaries), a cached row of 22,
+# experts of 12 and 7, a looped first layer
+CONFIG_I = plain.make_config([L(3, 10, 4, 6, 18, window=5, mlp=X(3, 2, 12, shared_ff=10)), W(2, 10, mlp=X(2, 1, 7)),
+                              L(2, 6, 2, 10, 5, window=None, scale=0.4)],
+                             width=52, vocab=41, streams=2, loop=(0, 1, 2), pair=(7, 3, 2), scale=1.5)
+CONFIGS = {"i": (CONFIG_I, 9, 5, 8), "h": (CONFIG_H, 8, 4, 16), "g": (CONFIG_G, 7, 4, 16), "a": (CONFIG_A, 1, 8, 16), "b": (CONFIG_B, 2, 4, 16), "c": (CONFIG_C, 3, 6, 8),     # config, seed, rank, page
            "d": (CONFIG_D, 4, 3, 32), "e": (CONFIG_E, 5, 5, 16), "f": (CONFIG_F, 6, 8, 16)}
 
 _FOLDERS, _TENSORS, _LOGITS, _SETTLED = {}, {}, {}, {}
@@ -209,7 +214,7 @@ def test_mixed_batches_reuse_pages_and_slots(which, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("which", ["e", "f", "h"])
+@pytest.mark.parametrize("which", ["e", "f", "h", "i"])
 def test_models_of_one_kind_of_layer(which, dtype):
     sequences = sequences_for(which, [70, 3, 131, 29, 64, 1], seed=70)
     check_replay(which, dtype, helpers.trace_whole(sequences), sequences, "whole")
@@ -344,7 +349,7 @@ def run_mixer(engine, block, layer, fed, tokens, cuts, name="x"):
 
 
 @pytest.mark.parametrize("dtype,tol", [("float32", 3e-6), ("bfloat16", 1.2e-2)])
-@pytest.mark.parametrize("which", ["a", "b", "c"])
+@pytest.mark.parametrize("which", ["a", "b", "c", "i"])
 def test_each_part_alone(which, dtype, tol):
     """Norm, both mixers, the feed-forward and the head, each fed with the plain implementation's own values.
     The mixers run a prompt in two portions, so the second one starts from pages and state."""
