@@ -61,7 +61,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
                          const int* __restrict__ block_table, int bt_stride, const int* __restrict__ item_row,
                          int first_item, int n_items, int n_heads, int n_kv_heads, int page_size, int window,
                          float scale_log2, SoftmaxExtras extras, const int* __restrict__ row_positions,
-                         int rows_per_item) {
+                         int rows_per_item, float* __restrict__ partial, int key_splits) {
     constexpr int RS = HD + 8;                         // padded row, in elements
     constexpr int CH = HD / 8;                         // 16-byte pieces of a row
     constexpr int KS = HD / 16;                        // k steps over the head dim
@@ -106,7 +106,15 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     const int tok0 = qs + qb * BQ;
     const int hi = pos0 + step * (rows - 1);                       // last key any row may see
     const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
-    const int kb_first = lo / BKEY, kb_last = hi / BKEY;
+    int kb_first = lo / BKEY, kb_last = hi / BKEY;
+    if (partial) {
+        // The key tiles of an item shared out over gridDim.z CTAs (rows of one position, few items: one CTA per item
+        // would walk all its tiles in turn while most SMs idle).  Each leaves its unnormalised sums and its softmax
+        // state in `partial`; a second kernel merges them in split order.
+        const int per = (kb_last - kb_first + key_splits) / key_splits;
+        kb_first += (int)blockIdx.z * per;
+        kb_last = min(kb_last, kb_first + per - 1);
+    }
     // the item's block-table row: item_row[item] where the table is kept by request slot, else the item itself
     const int* bt = block_table + (size_t)(item_row ? item_row[item] : item) * bt_stride;
 
@@ -280,6 +288,21 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
             o[dn][2] = o[dn][2] * s1 + pb.x * t1; o[dn][3] = o[dn][3] * s1 + pb.y * t1;
         }
     }
+    if (partial) {
+        // [item][split][row][HD + 2]: sums, then the running maximum (log2 units) and the denominator
+        float* mine = partial + (((size_t)(item - first_item) * key_splits + blockIdx.z) * q_len + qb * BQ) * (HD + 2);
+#pragma unroll
+        for (int dn = 0; dn < HD / 8; ++dn) {
+            const int d = dn * 8 + tq * 2;
+            if (row0 < rows) *reinterpret_cast<float2*>(mine + (size_t)row0 * (HD + 2) + d) = make_float2(o[dn][0], o[dn][1]);
+            if (row1 < rows) *reinterpret_cast<float2*>(mine + (size_t)row1 * (HD + 2) + d) = make_float2(o[dn][2], o[dn][3]);
+        }
+        if (tq == 0) {
+            if (row0 < rows) *reinterpret_cast<float2*>(mine + (size_t)row0 * (HD + 2) + HD) = make_float2(m_run[0], l_run[0]);
+            if (row1 < rows) *reinterpret_cast<float2*>(mine + (size_t)row1 * (HD + 2) + HD) = make_float2(m_run[1], l_run[1]);
+        }
+        return;
+    }
     // ---- normalise and store
     const float inv0 = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f, inv1 = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
 #pragma unroll
@@ -294,22 +317,58 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv
     }
 }
 
+// out[row] = sum over splits of partial sums, rescaled to the common maximum, over the summed denominators;
+// one CTA per row, a thread per number of the row.
+__global__ void merge_key_splits_kernel(const float* __restrict__ partial, int key_splits, int rows_per_item, int HD,
+                                        __nv_bfloat16* __restrict__ out, int out_stride) {
+    pdl_prologue();
+    partial = pdl_fresh(partial);
+    const int row = blockIdx.x, item = row / rows_per_item, r = row - item * rows_per_item;
+    const int width = HD + 2;
+    const float* base = partial + ((size_t)item * key_splits * rows_per_item + r) * width;
+    const size_t step = (size_t)rows_per_item * width;
+    float top = -INFINITY;
+    for (int s = 0; s < key_splits; ++s) top = fmaxf(top, base[s * step + HD]);
+    const float floor_ = top == -INFINITY ? 0.f : top;
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float sum = 0.f, denominator = 0.f;
+        for (int s = 0; s < key_splits; ++s) {
+            const float weight = exp2f(base[s * step + HD] - floor_);
+            denominator += base[s * step + HD + 1] * weight;
+            sum += base[s * step + d] * weight;
+        }
+        out[(size_t)row * out_stride + d] = __float2bfloat16_rn(denominator > 0.f ? sum / denominator : 0.f);
+    }
+}
+
 template <int HD>
 int launch(const void* q, int q_stride, void* out, int out_stride, const void* k_pool, const void* v_pool,
            long long page_stride, const int* q_start, const int* kv_len, const int* block_table, int bt_stride,
            const int* item_row, int first_item, int n_items, int max_blocks, int n_heads, int n_kv_heads,
            int page_size, int window, float scale, float softcap, const float* sink, cudaStream_t stream,
-           const int* row_positions = nullptr, int rows_per_item = 0) {
+           const int* row_positions = nullptr, int rows_per_item = 0, float* partial = nullptr, int key_splits = 1) {
     constexpr int RS = HD + 8;
     size_t smem = (size_t)(BQ + 8 * BKEY) * RS * 2;
     auto kernel = prefill_attention_kernel<HD>;
     static size_t raised[MAX_DEVICES] = {0};
     if (!ensure_dynamic_smem((const void*)kernel, smem, raised)) return PS_ERR_LAUNCH;
+    if (partial) {
+        const int status = launch_pdl(kernel, dim3(max_blocks, n_heads, key_splits), dim3(THREADS), smem, stream,
+                                      (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
+                                      (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_stride, q_start,
+                                      kv_len, block_table, bt_stride, item_row, first_item, n_items, n_heads,
+                                      n_kv_heads, page_size, window, scale * 1.4426950408889634f,
+                                      softmax_extras(scale, softcap, sink), row_positions, rows_per_item, partial,
+                                      key_splits);
+        if (status != PS_OK) return status;
+        return launch_pdl(merge_key_splits_kernel, dim3(n_items * rows_per_item), dim3(HD >= 64 ? 64 : 32), 0, stream,
+                          (const float*)partial, key_splits, rows_per_item, HD, (__nv_bfloat16*)out, out_stride);
+    }
     return launch_pdl(kernel, dim3(max_blocks, n_heads), dim3(THREADS), smem, stream, (const __nv_bfloat16*)q, q_stride,
                       (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
                       page_stride, q_start, kv_len, block_table, bt_stride, item_row, first_item, n_items, n_heads,
                       n_kv_heads, page_size, window, scale * 1.4426950408889634f, softmax_extras(scale, softcap, sink),
-                      row_positions, rows_per_item);
+                      row_positions, rows_per_item, (float*)nullptr, 1);
 }
 
 }  // namespace pf
@@ -353,12 +412,18 @@ PS_EXPORT int ps_prefill_attention(const void* q, int q_stride, void* out, int o
 // including that position (inside the window).  This is how the query heads of single tokens run when they all
 // read one key/value head: the heads of a token are the rows (q and out are [items * rows_per_item, head_dim]
 // with the given row strides), so every key is fetched once per token instead of once per head.
+// key_splits > 1 (at most 64 rows per item): the key tiles of an item are shared out over that many CTAs, which
+// leave their sums and softmax states in `partial` (float32 [items * key_splits * rows_per_item * (head_dim + 2)])
+// for a second kernel to merge.
 PS_EXPORT int ps_shared_position_attention(const void* q, int q_stride, void* out, int out_stride, const void* k_pool,
                                            const void* v_pool, long long page_stride, const int* row_positions,
                                            const int* block_table, int bt_stride, const int* item_row, int n_items,
                                            int rows_per_item, int head_dim, int page_size, int window, float scale,
-                                           void* stream) {
+                                           float* partial, int key_splits, void* stream) {
     if (n_items <= 0 || rows_per_item <= 0) return PS_OK;
+    if (key_splits < 1 || key_splits > 64 || (key_splits > 1 && (!partial || ((uintptr_t)partial & 7) || rows_per_item > 64)))
+        return PS_ERR_BAD_ARGUMENT;
+    if (key_splits == 1) partial = nullptr;
     if (!row_positions || !item_row || !block_table) return PS_ERR_BAD_ARGUMENT;
     if (head_dim <= 0 || head_dim % 16 != 0 || head_dim > 128) return PS_ERR_UNSUPPORTED;
     if (page_size <= 0 || page_size > 64 || (page_size & (page_size - 1))) return PS_ERR_UNSUPPORTED;
@@ -371,7 +436,7 @@ PS_EXPORT int ps_shared_position_attention(const void* q, int q_stride, void* ou
     case D:                                                                                                        \
         return ps::pf::launch<D>(q, q_stride, out, out_stride, k_pool, v_pool, page_stride, nullptr, nullptr,      \
                                  block_table, bt_stride, item_row, 0, n_items, blocks, 1, 1, page_size, window,    \
-                                 scale, 0.f, nullptr, s, row_positions, rows_per_item);
+                                 scale, 0.f, nullptr, s, row_positions, rows_per_item, partial, key_splits);
     switch (head_dim) {
         PS_PF_CASE(16) PS_PF_CASE(32) PS_PF_CASE(48) PS_PF_CASE(64)
         PS_PF_CASE(80) PS_PF_CASE(96) PS_PF_CASE(112) PS_PF_CASE(128)

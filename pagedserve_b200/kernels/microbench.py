@@ -258,7 +258,7 @@ def time_shared_position_attention(batch, context, heads, head_dim, page=16, win
     def run(i):
         layer = i % layers
         ops.shared_position_attention(q, out, pool[:, layer, 0], pool[:, layer, 0], stride, positions, table, rows,
-                                      heads, head_dim, page, window, head_dim ** -0.5)
+                                      heads, head_dim, page, window, head_dim ** -0.5, max_kv_len=context)
 
     seconds = _time(run, iters, graph=True)
     seen = min(context, window) if window else context

@@ -115,7 +115,7 @@ _SIGNATURES = {
                                               _F, _I, _I, _P, _P, _P, _P, _P],
         "ps_paged_attention_decode_ex": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I,
                                          _I, _I, _F, _I, _I, _I, _P, _P, _P, _P, _F, _P, _P],
-        "ps_shared_position_attention": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _P],
+        "ps_shared_position_attention": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _I, _P, _I, _I, _I, _I, _I, _F, _P, _I, _P],
         "ps_prefill_attention": [_P, _I, _P, _I, _P, _P, _L, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F,
                                  _F, _P, _P],
     },
@@ -724,22 +724,28 @@ class Ops:
         return out
 
     def shared_position_attention(self, q, out, k_pool, v_pool, page_stride, positions, block_table, token_row,
-                                  heads, head_dim, page_size, window, scale):
+                                  heads, head_dim, page_size, window, scale, max_kv_len=None):
         """Attention of single tokens whose ``heads`` query heads all read one key/value head (bfloat16, head
         sizes that are multiples of 16 up to 128): the heads of a token are the query rows of one tile, so its
         keys are fetched once.  ``q`` / ``out`` [T, heads * head_dim]; token t stands at ``positions[t]`` and
-        reads the pages of block-table row ``token_row[t]``."""
+        reads the pages of block-table row ``token_row[t]``.  With few tokens the key tiles of a token are shared
+        out over several CTAs (a rule of T and ``max_kv_len``, the longest context any token of the call may have)
+        whose partial results a second kernel merges."""
         T = q.shape[0]
         _require(q, "q", torch.bfloat16)
         _require(out, "out", torch.bfloat16)
         if (q.shape[1] != heads * head_dim or out.shape != q.shape or not q.is_contiguous()
                 or not out.is_contiguous()):
             raise KernelError("shared_position_attention: q and out must be contiguous [T, heads * head_dim]")
-        self.launches += 1
+        seen = min(max_kv_len, window) if (window and max_kv_len) else (max_kv_len or window or 0)
+        tiles = -(-seen // 64) + 1 if seen else 1                      # 64-key tiles a token can touch
+        splits = max(1, min(8, 296 // max(T, 1), tiles)) if heads <= 64 else 1
+        partial = self.empty((T * splits * heads * (head_dim + 2),), torch.float32, q.device) if splits > 1 else None
+        self.launches += 2 if splits > 1 else 1
         _check(self.fast.ps_shared_position_attention(
             _ptr(q), head_dim, _ptr(out), head_dim, _ptr(k_pool), _ptr(v_pool), page_stride, _ptr(positions),
             _ptr(block_table), block_table.stride(0), _ptr(token_row), T, heads, head_dim, page_size, window or 0,
-            scale, _stream()), "shared_position_attention")
+            scale, _ptr(partial), splits, _stream()), "shared_position_attention")
         return out
 
     @staticmethod

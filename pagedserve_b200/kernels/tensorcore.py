@@ -51,7 +51,7 @@ def linear(ops, a, w, bias, out, act=None, accumulate=False, status=None):
     return ops.linear_simt(a, w, bias, out, act, accumulate)
 
 
-SHARED_POSITION_FROM = 40      # short tokens of a step from which heads that share a key head run as query rows
+SHARED_POSITION_FROM = 8       # short tokens of a step from which heads that share a key head run as query rows
 
 
 def attention(ops, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, scale, softcap=None, sink=None):
@@ -67,13 +67,14 @@ def attention(ops, q, out, ctx, layer, n_heads, n_kv_heads, head_dim, window, sc
             and softcap is None and sink is None and q.is_contiguous() and out.is_contiguous():
         # Every query head reads the one key/value head: the heads of a token become the query rows of one
         # tile of the prompt kernel, all at the token's position, and the token's keys are fetched once instead
-        # of once per head (64 tokens x 1,024 keys, 16 heads on a row of 128: 88 us through the split-key kernel,
-        # 51 through this one).  One CTA per token walks all its keys in turn, which takes those 50 us whatever
-        # the number of tokens, so fewer tokens are better off with the split-key kernel's many CTAs (8 tokens:
-        # 17 us there); the two meet near 37 tokens.
+        # of once per head; with few tokens the key tiles of a token are shared out over up to 8 CTAs and merged
+        # by a second kernel.  16 heads on a row of 128, 1,024 keys (us, this / the split-key kernel per head):
+        # 64 tokens 35 / 88, 32 tokens 24 / 50, 16 tokens 14 / 28, 8 tokens 13.5 / 17 (512 keys: 12.8 / 11.7),
+        # 1 token 13 / 6: two launches and one round of a tile are a floor of about 13 us.
         ops.shared_position_attention(q[:short_tokens], out[:short_tokens], layer.k_pool, layer.v_pool,
                                       layer.page_stride, ctx.positions[:short_tokens], layer.block_table,
-                                      ctx.token_slot[:short_tokens], n_heads, head_dim, layer.page_size, window, scale)
+                                      ctx.token_slot[:short_tokens], n_heads, head_dim, layer.page_size, window, scale,
+                                      max_kv_len=ctx.max_kv_len)
     elif short_tokens:
         # The splits of a (token, head) pair merge through global memory. (With at most one pair per SM the
         # kernel makes one CTA of six teams per pair instead and merges in shared memory: batch 8, 278 -> 259 us
