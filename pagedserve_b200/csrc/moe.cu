@@ -68,7 +68,6 @@ moe_route_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ ro
     // of loads, all in flight together; partial sums meet in shared memory; warp 0 then holds the election.
     __shared__ float score[MOE_MAX_EXPERTS + 1];
     __shared__ float partial[MOE_WARPS][MOE_BATCH];
-    __shared__ unsigned char open[MOE_MAX_EXPERTS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
     if (raw) {
@@ -189,7 +188,6 @@ moe_route_kernel(const T* __restrict__ x, int x_stride, const T* __restrict__ ro
         mine[i] = e < E ? mine[i] * inv : -INFINITY;           // the softmax; -inf: no such expert
         if (e < E) {
             score[e] = mine[i];
-            open[e] = 1;
             dense[(size_t)t * E + e] = 0.f;
         }
     }
